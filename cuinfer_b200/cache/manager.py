@@ -35,9 +35,10 @@ class CacheGroupSpec:
     window: Optional[int] = None      # None: every token is kept
     planes: int = 2                   # rows of head_dim a head keeps per token: keys and values, or one shared row
     keep_first: int = 0               # with a window: the first so many tokens stay visible, so their pages stay held
+    chunked: bool = False             # the window is a chunk: position i sees the keys from i // window * window on
 
     def key(self) -> tuple:
-        return (self.num_kv_heads, self.head_dim, self.window, self.planes, self.keep_first)
+        return (self.num_kv_heads, self.head_dim, self.window, self.planes, self.keep_first, self.chunked)
 
 
 class PagePool:
@@ -221,8 +222,8 @@ class CacheManager:
         for g, spec in enumerate(self.groups):
             if spec.window is None:
                 continue
-            # the next query sits at position >= total and sees keys > total - window
-            first_needed = max(0, total - spec.window + 1)
+            # the next query sits at position >= total and sees keys > total - window (or, with chunks, its chunk)
+            first_needed = total // spec.window * spec.window if spec.chunked else max(0, total - spec.window + 1)
             first_page = first_needed // self.page_size
             table = held.tables[g]
             gone = []
@@ -282,10 +283,11 @@ class CacheManager:
 
 
 def group_runs(needs: Dict[int, "object"]) -> List[CacheGroupSpec]:
-    """Group runs by (kv heads, head size, window, planes, kept first tokens): runs with equal needs share pages ids and tables."""
+    """Group runs by (kv heads, head size, window, planes, kept first tokens, chunked): runs with equal needs share pages ids and tables."""
     by_key: Dict[tuple, List[int]] = {}
     for run in sorted(needs):
         n = needs[run]
         keep = getattr(n, "keep_first", 0) if n.window is not None else 0
-        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window, getattr(n, "planes", 2), keep), []).append(run)
-    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2], k[3], k[4]) for k, runs in by_key.items()]
+        chunked = bool(getattr(n, "chunked", False)) and n.window is not None
+        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window, getattr(n, "planes", 2), keep, chunked), []).append(run)
+    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2], k[3], k[4], k[5]) for k, runs in by_key.items()]

@@ -9,7 +9,10 @@
 //   * score = scale * q.k, then cap * tanh(score / cap) when cap > 0 (32-bit; tanh through the exponential);
 //   * a query at position i sees key j when j <= i and (window == 0 or i - j < window or j < keep_first): a tile walks
 //     the key tiles of the kept tokens that lie before its window (keys 0 .. min(keep_first, window start) - 1) and then
-//     those from its window's start to its last query.
+//     those from its window's start to its last query;
+//   * optional: a distance bias, score -= slope[head] * (i - j); a window that is a chunk (`chunked`: key j is seen
+//     when floor(j / window) == floor(i / window)); sinks, one score per head that joins the softmax's denominator and
+//     nothing else.
 // The softmax weights are rounded to bfloat16 for the second product; everything before that is 32-bit.
 #include "mma_utils.cuh"
 
@@ -51,7 +54,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                             const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ query_start_loc, const int* __restrict__ seq_lens,
                             int num_requests, int nq, int nkv, float scale, float cap, int window, int keep_first,
-                            int num_splits, float* __restrict__ partial) {
+                            int num_splits, float* __restrict__ partial, int chunked, const float* __restrict__ slopes,
+                            const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_req, s_tile;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -91,7 +95,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     const int last_row = min(row0 + kWmM, rows_total) - 1;
     const int pos_first = seq_len - n + row0 / g;
     const int pos_last = seq_len - n + last_row / g;
-    int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    auto window_start = [&](int pos) { return window > 0 ? (chunked ? pos / window * window : max(0, pos - window + 1)) : 0; };
+    int k_lo = window_start(pos_first);
     k_lo = k_lo / kWmN * kWmN;
     const int k_hi = pos_last + 1;
     const int kept_end = window > 0 ? min(keep_first, k_lo) : 0;
@@ -144,13 +149,16 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         }
     }
     __syncthreads();          // every warp has its query fragments: stage 1 may now take keys and values
-    int pos_row[2];
+    int pos_row[2], lo_row[2];
     bool row_ok[2];
+    float slope_row[2];          // the distance bias of the row's head, in base-2 units
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int grow = row0 + warp * 16 + qrow + 8 * h;
         row_ok[h] = grow < rows_total;
         pos_row[h] = row_ok[h] ? seq_len - n + grow / g : -1;
+        lo_row[h] = row_ok[h] ? window_start(pos_row[h]) : 0;
+        slope_row[h] = slopes && row_ok[h] ? slopes[kvh * g + grow % g] * kLog2e : 0.f;
     }
 
     // first and last position among this warp's rows: a key tile that every one of them sees whole needs no mask
@@ -197,7 +205,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
             }
         }
         const bool need_mask = !warp_full || (kept_tile ? key0 + kWmN > kept_end
-                                                        : (key0 + kWmN - 1 > warp_pos_min || (window > 0 && key0 <= warp_pos_max - window)));
+                                                        : (key0 + kWmN - 1 > warp_pos_min || (window > 0 && key0 < window_start(warp_pos_max))));
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) {
@@ -211,11 +219,12 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                     v = cap * (1.f - __fdividef(2.f, __expf(x) + 1.f));
                 }
                 v *= kLog2e;
+                const int key = key0 + nt * 8 + quad * 2 + (e & 1);
+                if (slopes) v -= slope_row[h] * (float)(pos_row[h] - key);
                 if (need_mask) {
-                    const int key = key0 + nt * 8 + quad * 2 + (e & 1);
                     const int pos = pos_row[h];
                     const bool vis = kept_tile ? (key < kept_end && pos >= 0)
-                                               : (key <= pos && (window <= 0 || key > pos - window || key < keep_first));
+                                               : (key <= pos && (window <= 0 || key >= lo_row[h] || key < keep_first));
                     v = vis ? v : -INFINITY;
                 }
                 s[nt][e] = v;
@@ -274,9 +283,16 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         if (!row_ok[h]) continue;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
         const int grow = row0 + warp * 16 + qrow + 8 * h;
         const int tl = grow / g, hi = grow % g;
+        float rescale = 1.f;
+        if (sinks && num_splits == 1) {                // the sink joins the denominator (the merge kernel adds it otherwise)
+            const float sink = sinks[kvh * g + hi] * kLog2e;
+            const float m_new = fmaxf(m_run[h], sink);
+            rescale = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+            l = l * rescale + exp2f(sink - m_new);
+        }
+        const float inv = (l > 0.f ? 1.f / l : 0.f) * rescale;
         if (num_splits > 1) {
             float* dst = partial + (((size_t)(q0 + tl) * nq + kvh * g + hi) * num_splits + blockIdx.z) * (DV + 2);
 #pragma unroll
@@ -300,14 +316,17 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
 
 // out[row] = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M) over the splits' partial results; a warp per (token, head).
 __global__ void window_attention_merge_kernel(const float* __restrict__ partial, int num_splits, int dv,
-                                              __nv_bfloat16* __restrict__ out, int out_stride, int nq, int rows) {
+                                              __nv_bfloat16* __restrict__ out, int out_stride, int nq, int rows,
+                                              const float* __restrict__ sinks) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const float* base = partial + (size_t)row * num_splits * (dv + 2);
     float M = -INFINITY;
     for (int i = 0; i < num_splits; ++i) M = fmaxf(M, base[(size_t)i * (dv + 2) + dv]);
-    float L = 0.f;
+    const float sink = sinks ? sinks[row % nq] * 1.4426950408889634f : -INFINITY;     // maxima are in base-2 units
+    M = fmaxf(M, sink);
+    float L = sinks ? exp2f(sink - M) : 0.f;
     for (int i = 0; i < num_splits; ++i) {
         const float mi = base[(size_t)i * (dv + 2) + dv];
         if (mi != -INFINITY) L += base[(size_t)i * (dv + 2) + dv + 1] * exp2f(mi - M);
@@ -328,7 +347,8 @@ template <int DK, int DV>
 static int launch_window_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
                              int page_size, const int* block_table, int table_stride, const int* query_start_loc,
                              const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, float cap,
-                             int window, int keep_first, int num_splits, float* partial, int num_tokens, cudaStream_t stream) {
+                             int window, int keep_first, int num_splits, float* partial, int num_tokens, int chunked,
+                             const float* slopes, const float* sinks, cudaStream_t stream) {
     const size_t smem = (size_t)(kWmStages * kWmN * (DK + DV)) * sizeof(__nv_bfloat16);
     static SmemLimit limit;
     if (int rc = raise_smem_limit(limit, window_attention_mma_kernel<DK, DV>, smem, "window_attention_mma")) return rc;
@@ -336,11 +356,11 @@ static int launch_window_mma(const void* q, int q_stride, void* out, int out_str
     window_attention_mma_kernel<DK, DV><<<grid, kWmWarps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
         page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv, scale, cap, window, keep_first,
-        num_splits, partial);
+        num_splits, partial, chunked, slopes, sinks);
     CIB_LAUNCH_CHECK("window_attention_mma");
     if (num_splits > 1) {
         const int rows = num_tokens * nq;
-        window_attention_merge_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(partial, num_splits, DV, (__nv_bfloat16*)out, out_stride, nq, rows);
+        window_attention_merge_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(partial, num_splits, DV, (__nv_bfloat16*)out, out_stride, nq, rows, sinks);
         CIB_LAUNCH_CHECK("window_attention_merge");
     }
     return 0;
@@ -357,11 +377,13 @@ extern "C" int cib_window_attention_mma_supports(int dim, int vdim, int nq, int 
 // num_tiles: the sum over requests of ceil(tokens_r * (nq / nkv) / 64), or any upper bound of it (CTAs that find no
 // tile leave).  num_splits > 1: every row tile's key tiles are shared out to so many CTAs, which leave float32 partial
 // results in `partial` ([tokens * nq][num_splits][vdim + 2]: output, running maximum, sum) for a second kernel to merge.
+// chunked: the window is a chunk (keys from floor(i / window) * window on); slopes, sinks: float32 [nq] or null.
 extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                         int num_pages, int page_size, const int* block_table, int table_stride,
                                         const int* query_start_loc, const int* seq_lens, int num_requests, int num_tiles,
                                         int nq, int nkv, int dim, int vdim, float scale, float cap, int window,
-                                        int keep_first, int num_splits, float* partial, int num_tokens, cudaStream_t stream) {
+                                        int keep_first, int num_splits, float* partial, int num_tokens, int chunked,
+                                        const float* slopes, const float* sinks, cudaStream_t stream) {
     CIB_REQUIRE(cib_window_attention_mma_supports(dim, vdim, nq, nkv), "window_attention_mma: sizes %d / %d are not taken by this kernel", dim, vdim);
     CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535, "window_attention_mma: bad sizes");
     CIB_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || partial), "window_attention_mma: %d splits need room for their partial results", num_splits);
@@ -373,7 +395,7 @@ extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, 
     if (dim == DKv && vdim == DVv)                                                                                           \
         return launch_window_mma<DKv, DVv>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, \
                                            query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, cap, window,     \
-                                           keep_first, num_splits, partial, num_tokens, stream)
+                                           keep_first, num_splits, partial, num_tokens, chunked, slopes, sinks, stream)
     CIB_WM(64, 32);
     CIB_WM(64, 64);
     CIB_WM(64, 128);

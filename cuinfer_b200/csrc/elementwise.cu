@@ -49,19 +49,19 @@ template <typename T> struct Vec<T, 1> {
 template <typename T, int V>
 __global__ void embedding_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
-                                        int* __restrict__ bad_flag, float scale) {
+                                        int* __restrict__ bad_flag, float scale, int copies) {
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
     if (!ok && threadIdx.x == 0 && bad_flag) atomicExch(bad_flag, 1);
     const T* src = table + (size_t)(ok ? id : 0) * hidden;
-    float* dst = out + (size_t)t * hidden;
+    float* dst = out + (size_t)t * copies * hidden;        // a residual of several streams starts with every stream equal
     for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
         float v[V];
         Vec<T, V>::load(src + i, v);
 #pragma unroll
         for (int k = 0; k < V; ++k) v[k] = ok ? v[k] * scale : 0.f;
-        Vec<float, V>::store(dst + i, v);
+        for (int c = 0; c < copies; ++c) Vec<float, V>::store(dst + (size_t)c * hidden + i, v);
     }
 }
 
@@ -183,7 +183,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ residual, const TD*
 // act[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j], silu(g) = g / (1 + exp(-g)), in 32 bits with the
 // exact exponential.
 template <typename T, int V>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int inter, int rows) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int inter, int rows, int gelu) {
     const int per_row = inter / V;
     const size_t total = (size_t)rows * per_row;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
@@ -194,7 +194,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ a
         Vec<T, V>::load(gate_up + t * 2 * inter + j, g);
         Vec<T, V>::load(gate_up + t * 2 * inter + inter + j, u);
 #pragma unroll
-        for (int k = 0; k < V; ++k) g[k] = g[k] / (1.f + expf(-g[k])) * u[k];
+        for (int k = 0; k < V; ++k)
+            g[k] = (gelu ? 0.5f * g[k] * (1.f + tanhf(0.7978845608028654f * (g[k] + 0.044715f * g[k] * g[k] * g[k])))
+                         : g[k] / (1.f + expf(-g[k]))) * u[k];
         Vec<T, V>::store(act + t * inter + j, g);
     }
 }
@@ -263,19 +265,19 @@ static inline int norm_threads(int hidden, int vec) {
 }
 
 extern "C" int cib_embedding_gather(const int* ids, const void* table, int table_dtype, float* out,
-                                    int num_tokens, int hidden, int vocab, int* bad_flag, float scale,
+                                    int num_tokens, int hidden, int vocab, int* bad_flag, float scale, int copies,
                                     cudaStream_t stream) {
-    CIB_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0, "embedding_gather: bad sizes T=%d H=%d V=%d",
+    CIB_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0 && copies >= 1, "embedding_gather: bad sizes T=%d H=%d V=%d",
                 num_tokens, hidden, vocab);
     if (num_tokens == 0) return 0;
     const bool v4 = hidden % 4 == 0;
     const int threads = norm_threads(hidden, v4 ? 4 : 1) > 256 ? 256 : norm_threads(hidden, v4 ? 4 : 1);
     if (table_dtype == kF32) {
-        if (v4) embedding_gather_kernel<float, 4><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale);
-        else embedding_gather_kernel<float, 1><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale);
+        if (v4) embedding_gather_kernel<float, 4><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale, copies);
+        else embedding_gather_kernel<float, 1><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale, copies);
     } else if (table_dtype == kBF16) {
-        if (v4) embedding_gather_kernel<__nv_bfloat16, 4><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale);
-        else embedding_gather_kernel<__nv_bfloat16, 1><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale);
+        if (v4) embedding_gather_kernel<__nv_bfloat16, 4><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale, copies);
+        else embedding_gather_kernel<__nv_bfloat16, 1><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale, copies);
     } else {
         CIB_REQUIRE(false, "embedding_gather: unsupported table dtype %d", table_dtype);
     }
@@ -331,7 +333,8 @@ extern "C" int cib_gather_rows(const float* residual, const void* delta, int del
     return 0;
 }
 
-extern "C" int cib_silu_mul(const void* gate_up, void* act, int dtype, int rows, int inter, cudaStream_t stream) {
+// gelu != 0: the gate goes through the tanh form of GELU instead of SiLU (exact tangent).
+extern "C" int cib_silu_mul(const void* gate_up, void* act, int dtype, int rows, int inter, int gelu, cudaStream_t stream) {
     CIB_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d I=%d", rows, inter);
     if (rows == 0) return 0;
     const bool v4 = inter % 4 == 0;
@@ -339,11 +342,11 @@ extern "C" int cib_silu_mul(const void* gate_up, void* act, int dtype, int rows,
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == kF32) {
-        if (v4) silu_mul_kernel<float, 4><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)act, inter, rows);
-        else silu_mul_kernel<float, 1><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)act, inter, rows);
+        if (v4) silu_mul_kernel<float, 4><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)act, inter, rows, gelu);
+        else silu_mul_kernel<float, 1><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)act, inter, rows, gelu);
     } else if (dtype == kBF16) {
-        if (v4) silu_mul_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, inter, rows);
-        else silu_mul_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, inter, rows);
+        if (v4) silu_mul_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, inter, rows, gelu);
+        else silu_mul_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, inter, rows, gelu);
     } else {
         CIB_REQUIRE(false, "silu_mul: unsupported dtype %d", dtype);
     }

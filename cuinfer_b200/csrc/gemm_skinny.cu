@@ -38,6 +38,7 @@ struct SkinnyArgs {
     const void* warm; unsigned long long warm_bytes;         // the weights of the kernel after this one (or null): fetched into L2
     int norm_w_offset;                                       // byte offset of the norm gains' copy in shared memory
     int inbox_offset;                                        // CS > 1: byte offset of the first CTA's slots for the others' sums
+    int gate_gelu;                                           // kSiluPair: the gate is the tanh form of GELU instead of SiLU
 };
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
@@ -307,8 +308,9 @@ skinny_gemm_kernel(const SkinnyArgs a) {
             }
             const int n = tile_block * 16 + nl;
             if (n < a.up_offset)
-                reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + n] =
-                    __float2bfloat16_rn(gsum / (1.f + expf(-gsum)) * usum);
+                reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + n] = __float2bfloat16_rn(
+                    (a.gate_gelu ? 0.5f * gsum * (1.f + tanhf(0.7978845608028654f * (gsum + 0.044715f * gsum * gsum * gsum)))
+                                 : gsum / (1.f + expf(-gsum))) * usum);
         }
     } else {
         for (int idx = tid; idx < RT * 16 * kCols; idx += kSkWarps * 32) {
@@ -429,7 +431,7 @@ extern "C" int cib_gemm_skinny_supports(int M, int N, int K, int with_norm) {
 // act: [M, K] bfloat16 rows (lda), or null when res_in is given: then the activations are
 // RMSNorm(res_in + pending) * norm_w computed in the kernel, and res_out (if not null) receives res_in + pending.
 // epilogue: 0 = bfloat16 out[M, N]; 1 = float32 out[M, N]; 2 = rows [0, up_offset) are gates and rows
-// [up_offset, N) the matching ups: out[M, up_offset] = silu(gate) * up in bfloat16.
+// [up_offset, N) the matching ups: out[M, up_offset] = silu(gate) * up in bfloat16; 3 = the same with gelu_tanh(gate).
 // warm / warm_bytes: memory that the kernel after this one reads first (its weights), or null: fetched into the L2 meanwhile.
 extern "C" int cib_gemm_skinny(const void* w, int ldw, int N, int K, const void* act, int lda, const float* res_in,
                                const void* pending, int pending_dtype, const void* norm_w, int norm_w_dtype, float eps,
@@ -440,7 +442,9 @@ extern "C" int cib_gemm_skinny(const void* w, int ldw, int N, int K, const void*
     CIB_REQUIRE((act != nullptr) != (res_in != nullptr), "gemm_skinny: give plain activations or a residual to normalise");
     CIB_REQUIRE(act == nullptr || (lda >= K && lda % 8 == 0 && ((uintptr_t)act % 16) == 0), "gemm_skinny: activation rows must be 16-byte aligned");
     CIB_REQUIRE(res_in == nullptr || (norm_w != nullptr && K % 4 == 0 && res_out != res_in), "gemm_skinny: the norm needs its weight and a second residual buffer");
-    CIB_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_skinny: unknown epilogue %d", epilogue);
+    CIB_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_skinny: unknown epilogue %d", epilogue);
+    const int gate_gelu = epilogue == 3;           // 3: as 2 with the tanh form of GELU as the gate
+    if (gate_gelu) epilogue = kSiluPair;
     CIB_REQUIRE(epilogue != kSiluPair || (up_offset > 0 && 2 * up_offset == N && ldo >= up_offset), "gemm_skinny: a gate/up pair needs N = 2 * up_offset");
     CIB_REQUIRE(epilogue == kSiluPair || ldo >= N, "gemm_skinny: ldo too small");
     SkinnyArgs a;
@@ -448,7 +452,7 @@ extern "C" int cib_gemm_skinny(const void* w, int ldw, int N, int K, const void*
     a.act = (const __nv_bfloat16*)act; a.lda = lda;
     a.res_in = res_in; a.pending = pending; a.pending_bf16 = pending_dtype == kBF16;
     a.norm_w = AnyVec{norm_w, norm_w_dtype == kBF16}; a.eps = eps; a.res_out = res_out;
-    a.out = out; a.ldo = ldo; a.M = M; a.up_offset = up_offset; a.act_stride = 0;
+    a.out = out; a.ldo = ldo; a.M = M; a.up_offset = up_offset; a.act_stride = 0; a.gate_gelu = gate_gelu;
     a.warm = ((uintptr_t)warm % 16) == 0 && warm_bytes > 0 ? warm : nullptr;
     a.warm_bytes = a.warm ? (unsigned long long)warm_bytes : 0;
     if (M <= 8) return dispatch_skinny<1>(a, epilogue, use_pdl, stream);

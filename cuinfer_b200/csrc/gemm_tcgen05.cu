@@ -40,7 +40,7 @@ struct TcSmem {
 // PAIR: launched as clusters of two CTAs that share each 256 x BN tile (see the helpers above).  Per 64-k step a CTA
 // then fetches 16 KB of activations and BN / 2 weight rows instead of BN: the kernel is bound by what an SM can fetch
 // from the L2, so fewer bytes per flop is what makes it faster.
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false, bool PAIR = false>
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, int SILU = 0, bool PAIR = false>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out, int ldo, int M, int N, int K,
@@ -213,8 +213,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             // 1024 product went from 26 to 40 us).  The two approximations are good to about 2^-21
                             // relative, far inside the 2^-9 of the bfloat16 rounding that follows; exp overflowing to
                             // infinity for g < -88 gives g / inf = -0, the limit
+                            // SILU == 2: the tanh form of GELU, g (1 + tanh z) / 2 = g / (1 + exp(-2 z)) with
+                            // z = sqrt(2 / pi) (g + 0.044715 g^3): the same shape with another exponent
+                            const float arg = SILU == 2 ? -2.f * 0.7978845608028654f * fmaf(0.044715f * g * g, g, g) : -g;
                             float ex;
-                            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(-g * 1.4426950408889634f));
+                            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(arg * 1.4426950408889634f));
                             y[e] = __fdividef(g, 1.f + ex) * u;
                         }
                         uint4 pk;
@@ -343,7 +346,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
     return tc_make_map(map, base, rows, K, ld, box_rows, "gemm_tcgen05");
 }
 
-template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, bool SILU = false, bool PAIR = false>
+template <int BN, int STAGES, bool F32OUT, bool TMA_STORE, int SILU = 0, bool PAIR = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, void* out, int ldo, int M, int N,
                      int K, int* error_flag, cudaStream_t stream, int up_offset = 0) {
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, F32OUT, TMA_STORE, SILU, PAIR>;
@@ -403,7 +406,8 @@ extern "C" int cib_gemm_tcgen05_supports(int M, int N, int K) {
 
 // a: [M, K] bfloat16 rows (lda), w: [N, K] bfloat16 rows (ldw), out: [M, N] bfloat16 (out_f32 = 0) or float32.
 // error_flag: one int in device memory, zero before the call; non-zero afterwards means a bounded wait gave up.
-// silu_pair: w holds N / 2 gate rows followed by N / 2 up rows and out is [M, N / 2] bfloat16 = silu(a gate^T) * (a up^T).
+// silu_pair: w holds N / 2 gate rows followed by N / 2 up rows and out is [M, N / 2] bfloat16 = act(a gate^T) * (a up^T),
+// act = SiLU (1) or the tanh form of GELU (2).
 extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int out_f32, int silu_pair,
                                 int M, int N, int K, int* error_flag, cudaStream_t stream) {
     CIB_REQUIRE(cib_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
@@ -424,8 +428,12 @@ extern "C" int cib_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, 
         if (make_map(&ma, a, M, K, lda, kTcBM) != 0 || make_map(&mw, w, N, K, ldw, 128) != 0 ||
             make_map(&mo, out, M, half, ldo, kTcBM) != 0)
             return -1;
-        if (pair) return launch_tc<256, 6, false, true, true, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
-        return launch_tc<256, 4, false, true, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+        if (silu_pair == 2) {       // the gate is the tanh form of GELU
+            if (pair) return launch_tc<256, 6, false, true, 2, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+            return launch_tc<256, 4, false, true, 2>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+        }
+        if (pair) return launch_tc<256, 6, false, true, 1, true>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
+        return launch_tc<256, 4, false, true, 1>(ma, mw, mo, out, ldo, M, N, K, error_flag, stream, half);
     }
     if (pair) {
         // 256 x 256 tiles when those still give most pairs a tile, else 256 x 128; a CTA loads half of a tile's weight rows

@@ -67,7 +67,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 def _declare(lib: ctypes.CDLL) -> None:
     sig = {
-        "cib_embedding_gather": [_P, _P, _I, _P, _I, _I, _I, _P, _F, _P],
+        "cib_embedding_gather": [_P, _P, _I, _P, _I, _I, _I, _P, _F, _I, _P],
         "cib_sandwich_layernorm": [_P, _P, _I, _P, _P, _F, _P, _P, _P, _F, _I, _P, _I, _I, _I, _P],
         "cib_relu_squared": [_P, _P, _I, ctypes.c_longlong, _P],
         "cib_sigmoid_gate": [_P, _I, _P, _I, _P, _I, _I, _I, _P],
@@ -81,9 +81,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
         "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
         "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _I, _I, _P],
-        "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I, _P],
-        "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
-        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _P],
+        "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I,
+                                      _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _P, _P],
+        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _I, _P, _P, _P],
+        "cib_hyper_stream": [_P, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _P],
+        "cib_hyper_gather": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
         "cib_delta_prep": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
         "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
@@ -93,7 +96,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_gelu_tanh": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _P],
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
-        "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
+        "cib_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
         "cib_qk_norm_rope_kv_write": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _F, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P, ctypes.c_longlong, _P],
@@ -182,14 +185,16 @@ def _count() -> None:
 
 def embedding_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, bad_flag: torch.Tensor | None = None,
                      scale: float = 1.0) -> None:
-    """out[t] = table[ids[t]] * scale as float32 rows."""
+    """out[t] = table[ids[t]] * scale as float32 rows; an ``out`` of shape [T, S, H] gets the row S times (a residual
+    of several streams starts with every stream equal)."""
     T = ids.numel()
     V, H = table.shape
-    if out.shape != (T, H):
-        raise KernelError(f"embedding_gather: out must be [{T}, {H}], got {list(out.shape)}")
+    copies = out.shape[1] if out.dim() == 3 else 1
+    if out.shape not in ((T, H), (T, copies, H)):
+        raise KernelError(f"embedding_gather: out must be [{T}, {H}] or [{T}, S, {H}], got {list(out.shape)}")
     rc = library().cib_embedding_gather(
         _cuda(ids, "ids", torch.int32), _cuda(table, "table"), _code(table, "table"), _cuda(out, "out", torch.float32),
-        T, H, V, _cuda(bad_flag, "bad_flag", torch.int32) if bad_flag is not None else None, float(scale), _stream())
+        T, H, V, _cuda(bad_flag, "bad_flag", torch.int32) if bad_flag is not None else None, float(scale), copies, _stream())
     _check(rc, "embedding_gather")
     _count()
 
@@ -278,13 +283,13 @@ def gather_rows(residual: torch.Tensor, delta: torch.Tensor | None, indices: tor
     _count()
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, gelu: bool = False) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]; ``gelu``: the tanh form of GELU in the place of SiLU."""
     rows, two_i = gate_up.shape
     inter = two_i // 2
     if two_i != 2 * inter or out.shape != (rows, inter) or out.dtype != gate_up.dtype:
         raise KernelError(f"silu_mul: gate_up {list(gate_up.shape)} / out {list(out.shape)} do not fit")
-    rc = library().cib_silu_mul(_cuda(gate_up, "gate_up"), _cuda(out, "out"), _code(gate_up, "gate_up"), rows, inter, _stream())
+    rc = library().cib_silu_mul(_cuda(gate_up, "gate_up"), _cuda(out, "out"), _code(gate_up, "gate_up"), rows, inter, 1 if gelu else 0, _stream())
     _check(rc, "silu_mul")
     _count()
 
@@ -709,6 +714,7 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: tor
 use_pdl = os.environ.get("CUINFER_B200_PDL", "1") != "0"
 
 EPILOGUE_BF16, EPILOGUE_F32, EPILOGUE_SILU_PAIR = 0, 1, 2
+EPILOGUE_GELU_PAIR = 3          # as the SiLU pair, with the tanh form of GELU as the gate
 
 
 def gemm_skinny_supports(M: int, N: int, K: int, with_norm: bool = False) -> bool:
@@ -732,7 +738,7 @@ def gemm_skinny(w: torch.Tensor, out: torch.Tensor, *, act: torch.Tensor | None 
     if w.dtype != torch.bfloat16 or w.stride(1) != 1:
         raise KernelError("gemm_skinny: weights must be bfloat16 with dense rows")
     if silu_pair:
-        epi = EPILOGUE_SILU_PAIR
+        epi = EPILOGUE_GELU_PAIR if silu_pair == "gelu_tanh" else EPILOGUE_SILU_PAIR
         if out.dtype != torch.bfloat16 or out.shape[1] * 2 != N:
             raise KernelError("gemm_skinny: a gate/up pair writes bfloat16 [M, N/2]")
     else:
@@ -902,7 +908,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, silu_pair:
     rc = library().cib_gemm_tcgen05(
         _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0),
         _cuda(out, "out", contiguous=False), out.stride(0), 1 if out.dtype == torch.float32 else 0,
-        1 if silu_pair else 0, M, N, K, _error_flag(a.device).data_ptr(), _stream())
+        (2 if silu_pair == "gelu_tanh" else 1) if silu_pair else 0, M, N, K, _error_flag(a.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
     note_flagged_launch()
     _count()
@@ -1004,14 +1010,31 @@ def router_topk(logits: torch.Tensor, top: int, choice: torch.Tensor, weight: to
 
 # ---- attention with a capped score and a window that keeps the first tokens ---------------------------------------------------
 
+def _f32_vec(t: torch.Tensor | None, n: int, what: str):
+    """Pointer of an optional float32 vector of ``n`` values (None -> null)."""
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or t.numel() != n:
+        raise KernelError(f"{what} must be float32 with {n} values, got {t.dtype} with {t.numel()}")
+    return _cuda(t, what)
+
+
 def window_attention_prep(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
                           freq: torch.Tensor | None, rot_dims: int, eps: float, num_heads: int, num_kv_heads: int, dim: int,
-                          vdim: int, v_first: torch.Tensor | None, mix: torch.Tensor | None, cache: torch.Tensor | None) -> None:
-    """On the packed rows ``[q | k | v]``: rotary encoding (neighbouring pairs, the first ``rot_dims`` values, 32-bit
-    angle ``pos * freq[i]``) and unit RMS of every query and key head; queries are rewritten in place; keys and values
+                          vdim: int, v_first: torch.Tensor | None, mix: torch.Tensor | None, cache: torch.Tensor | None, *,
+                          bias: torch.Tensor | None = None, norm: bool = True, q_gain: torch.Tensor | None = None,
+                          k_gain: torch.Tensor | None = None, norm_first: bool = False, rot_half: bool = False,
+                          q_temp: tuple | None = None) -> None:
+    """On the packed rows ``[q | k | v]``: ``bias`` (float32, one value per column) is added; rotary encoding of the
+    first ``rot_dims`` values of every query and key head (32-bit angle ``pos * freq[i]``; neighbouring pairs, or with
+    ``rot_half`` the pairs (i, i + rot_dims / 2)); with ``norm`` every query and key head is divided by its root mean
+    square and multiplied by ``q_gain`` / ``k_gain`` (float32 [dim], None: no gain), after the rotation or, with
+    ``norm_first``, before it; ``q_temp = (coef, every)`` multiplies the queries by
+    ``1 + coef * ln(floor((pos + 1) / every) + 1)``.  Queries are rewritten in place; keys and values
     (``(1 - mix) * v + mix * v_first`` when both are given) go to ``cache[page, 0, kv head, slot, dim + vdim]``."""
     T, stride = qkv.shape
-    if stride < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim or qkv.stride(1) != 1:
+    columns = (num_heads + num_kv_heads) * dim + num_kv_heads * vdim
+    if stride < columns or qkv.stride(1) != 1:
         raise KernelError("window_attention_prep: rows are too short")
     if cache is not None:
         if cache.dim() != 5 or cache.shape[1] != 1 or cache.shape[2] != num_kv_heads or cache.shape[4] != dim + vdim or cache.dtype != qkv.dtype:
@@ -1030,16 +1053,22 @@ def window_attention_prep(qkv: torch.Tensor, positions: torch.Tensor, slot_mappi
         _cuda(v_first, "v_first", contiguous=False) if v_first is not None else None, v_first.stride(0) if v_first is not None else 0,
         _cuda(mix, "mix") if mix is not None else None, _code(mix, "mix") if mix is not None else 0,
         _cuda(cache, "cache") if cache is not None else None, cache.shape[0] * cache.shape[3] if cache is not None else 0,
-        cache.shape[3] if cache is not None else 1, T, _stream())
+        cache.shape[3] if cache is not None else 1, T,
+        _f32_vec(bias, columns, "bias"), _f32_vec(q_gain, dim, "q_gain"), _f32_vec(k_gain, dim, "k_gain"), 1 if norm else 0,
+        1 if norm_first else 0, 1 if rot_half else 0, 1 if q_temp else 0, float(q_temp[0]) if q_temp else 0.0,
+        int(q_temp[1]) if q_temp else 1, _stream())
     _check(rc, "window_attention_prep")
     _count()
 
 
 def window_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                              positions: torch.Tensor, token_request: torch.Tensor, num_heads: int, num_kv_heads: int,
-                             dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
+                             dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int, *,
+                             chunked: bool = False, slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> None:
     """Attention of the query rows ``q[:, :H * dim]`` over the paged cache of [key | value] rows; ``out`` [T, H * vdim].
-    ``softcap`` 0: no cap; ``window`` 0: every earlier key."""
+    ``softcap`` 0: no cap; ``window`` 0: every earlier key; ``chunked``: the window is a chunk, key j is seen when
+    ``j // window == i // window``; ``slopes`` (float32 [H]): ``score -= slope * (i - j)``; ``sinks`` (float32 [H]): a
+    score per head that joins the softmax's denominator and nothing else."""
     T = q.shape[0]
     if q.stride(1) != 1 or out.shape != (T, num_heads * vdim) or out.dtype != q.dtype or cache.dtype != q.dtype or not out.is_contiguous():
         raise KernelError("window_attention: out/cache do not fit q")
@@ -1047,7 +1076,8 @@ def window_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Te
         _cuda(q, "q", contiguous=False), _code(q, "q"), q.stride(0), _cuda(out, "out"), out.stride(0), _cuda(cache, "cache"),
         cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
         _cuda(positions, "positions", torch.int32), _cuda(token_request, "token_request", torch.int32), T, num_heads,
-        num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _stream())
+        num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0),
+        1 if chunked and window else 0, _f32_vec(slopes, num_heads, "slopes"), _f32_vec(sinks, num_heads, "sinks"), _stream())
     _check(rc, "window_attention_generic")
     _count()
 
@@ -1058,11 +1088,13 @@ def window_attention_mma_supports(dim: int, vdim: int, num_heads: int, num_kv_he
 
 def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                          query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens, num_heads: int, num_kv_heads: int,
-                         dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int, splits: int = 1) -> None:
+                         dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int, splits: int = 1, *,
+                         chunked: bool = False, slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> None:
     """The same attention on the tensor cores (bfloat16; key sizes 64 or 128, value sizes 32, 64 or 128).  ``query_lens``:
     tokens per request as host integers, or an upper bound that holds for every batch a captured step replays; they size
     the launch only.  ``splits`` > 1: the key tiles of every row tile are shared out to so many CTAs and a second kernel
-    merges their partial results (decode steps over long windows, where a request has one row tile per key head)."""
+    merges their partial results (decode steps over long windows, where a request has one row tile per key head).
+    ``chunked``, ``slopes``, ``sinks``: as for the all-sizes kernel."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or q.stride(1) != 1 or out.shape != (T, num_heads * vdim) or out.dtype != q.dtype or cache.dtype != q.dtype:
         raise KernelError("window_attention_mma: bfloat16 rows, out [T, H * vdim]")
@@ -1075,7 +1107,8 @@ def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
         cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
         _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32), seq_lens.numel(), tiles,
         num_heads, num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), splits,
-        _cuda(partial, "partial") if partial is not None else None, T, _stream())
+        _cuda(partial, "partial") if partial is not None else None, T, 1 if chunked and window else 0,
+        _f32_vec(slopes, num_heads, "slopes"), _f32_vec(sinks, num_heads, "sinks"), _stream())
     _check(rc, "window_attention_mma")
     _count()
     if splits > 1:
@@ -1167,4 +1200,53 @@ def head_rms_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: 
         _code(gain, "gain"), 1 if gain.numel() != vdim else 0, float(eps), 1 if silu else 0,
         _cuda(out, "out"), num_heads, vdim, T, _stream())
     _check(rc, "head_rms_gate")
+    _count()
+
+
+# ---- a residual of several streams ---------------------------------------------------------------------------------------------
+
+def hyper_stream(streams: torch.Tensor, y: torch.Tensor | None, write: tuple | None, read: torch.Tensor | None,
+                 norm: tuple | None, out: torch.Tensor | None, read_out: torch.Tensor | None = None) -> None:
+    """One pass over the 32-bit residual streams ``[T, S, W]``.  ``write = (mix [S, S], out [S])`` with the sub-layer
+    output ``y`` [T, W]: every stream is rewritten from the old ones, ``x_t = sum_s mix[s, t] x_s + out[t] y``.
+    ``read`` [S]: the next sub-layer's input ``u = sum_t read[t] x_t``; ``out`` gets its RMS norm times the gain
+    (``norm = (gain or None, eps)``) in its dtype and ``read_out`` (float32) the row ``u`` itself.  Coefficients are
+    float32."""
+    T, S, W = streams.shape
+    if (y is None) != (write is None):
+        raise KernelError("hyper_stream: a write needs the sub-layer's output and its coefficients")
+    if y is not None and (y.shape != (T, W) or not y.is_contiguous()):
+        raise KernelError(f"hyper_stream: y must be [{T}, {W}], got {list(y.shape)}")
+    if (out is not None or read_out is not None) and read is None:
+        raise KernelError("hyper_stream: a read needs its coefficients")
+    if out is not None and (norm is None or out.shape != (T, W)):
+        raise KernelError("hyper_stream: the normed rows need (gain, eps) and the shape [T, W]")
+    if read_out is not None and read_out.shape != (T, W):
+        raise KernelError("hyper_stream: read_out must be [T, W]")
+    gain = norm[0] if norm else None
+    if gain is not None and gain.numel() != W:
+        raise KernelError(f"hyper_stream: the gain must have {W} values")
+    rc = library().cib_hyper_stream(
+        _cuda(streams, "streams", torch.float32), _cuda(y, "y") if y is not None else None, _code(y, "y") if y is not None else 0,
+        _f32_vec(write[0], S * S, "mix") if write else None, _f32_vec(write[1], S, "out coefficients") if write else None,
+        _f32_vec(read, S, "read coefficients"), _cuda(gain, "gain") if gain is not None else None,
+        _code(gain, "gain") if gain is not None else 0, float(norm[1]) if norm else 0.0,
+        _cuda(out, "out") if out is not None else None, _code(out, "out") if out is not None else 0,
+        _cuda(read_out, "read_out", torch.float32) if read_out is not None else None, S, W, T, _stream())
+    _check(rc, "hyper_stream")
+    _count()
+
+
+def hyper_gather(streams: torch.Tensor, y: torch.Tensor | None, write: tuple | None, indices: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = the sum over the streams of token ``indices[r]``, after the outstanding write ``(y, (mix, out))`` if
+    there is one; the other tokens' rows are not touched."""
+    T, S, W = streams.shape
+    n = indices.numel()
+    if out.shape != (n, W) or (y is None) != (write is None) or (y is not None and y.shape != (T, W)):
+        raise KernelError("hyper_gather: shapes do not fit")
+    rc = library().cib_hyper_gather(
+        _cuda(streams, "streams", torch.float32), _cuda(y, "y") if y is not None else None, _code(y, "y") if y is not None else 0,
+        _f32_vec(write[0], S * S, "mix") if write else None, _f32_vec(write[1], S, "out coefficients") if write else None,
+        _cuda(indices, "indices", torch.int32), _cuda(out, "out", torch.float32), S, W, T, n, _stream())
+    _check(rc, "hyper_gather")
     _count()

@@ -5,7 +5,7 @@ from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, 
 from .spec import LayerSpec, ModelSpec, PagedCacheNeed, PartSpec, StateNeed, TensorSpec
 
 # importing the built-in parts registers them
-from . import attention, block, feed_forward, latent_attention, norm, position, recurrent, token_side, window_attention  # noqa: E402,F401
+from . import attention, block, feed_forward, hyper, latent_attention, norm, position, recurrent, token_side, window_attention  # noqa: E402,F401
 from .model import DecoderModel, build_layer  # noqa: E402
 
 __all__ = [

@@ -93,8 +93,11 @@ _FORCE_GENERIC_WINDOW = os.environ.get("CUINFER_B200_WINDOW_ATTENTION", "") == "
 
 
 def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int, num_kv_heads: int,
-                     dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
-    """Attention over cached [key | value] rows with a capped score and a window that keeps the first tokens: bfloat16
+                     dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int, *, chunked: bool = False,
+                     slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> None:
+    """Attention over cached [key | value] rows with a capped score and a window that keeps the first tokens (or, with
+    ``chunked``, a mask of chunks; ``slopes``: a distance bias per head; ``sinks``: a score per head in the softmax's
+    denominator): bfloat16
     steps whose sizes the tensor-core kernel takes run there, decode steps too (the window's 64-key tiles shared out to
     several CTAs, see ``window_decode_splits``; the all-sizes kernel, a warp per token and head with one key per lane,
     measured 16 times slower at a window of 1 024 keys of 128 values); float32 and every other size run the all-sizes kernel.  ``CUINFER_B200_WINDOW_ATTENTION=generic``
@@ -103,7 +106,9 @@ def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepC
             and kernels.window_attention_mma_supports(dim, vdim, num_heads, num_kv_heads)):
         kernels.window_attention_mma(q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                      ctx.query_lens_for_launch(), num_heads, num_kv_heads, dim, vdim, scale, softcap, window, keep_first,
-                                     splits=window_decode_splits(ctx, num_kv_heads, window, keep_first))
+                                     splits=window_decode_splits(ctx, num_kv_heads, window, keep_first), chunked=chunked,
+                                     slopes=slopes, sinks=sinks)
         return
     kernels.window_attention_generic(q, out, kv.cache, kv.group.block_table, ctx.positions, ctx.token_request, num_heads,
-                                     num_kv_heads, dim, vdim, scale, softcap, window, keep_first)
+                                     num_kv_heads, dim, vdim, scale, softcap, window, keep_first, chunked=chunked,
+                                     slopes=slopes, sinks=sinks)

@@ -32,9 +32,13 @@ class ResidualStream:
     pending rows go through BEFORE they are added (a layer that norms a sub-layer's output), and ``extra``, 32-bit
     rows that are added as well (a model that feeds its embedding output in again).  A norm that can do all of it in
     its own pass does; anything else calls ``settle()`` first, after which only ``residual`` counts.
+
+    A residual of several streams per token (``residual`` is [T, S, W]) is written to by learned coefficients instead of
+    a sum: ``pending`` then waits together with ``writer``, the part that knows how it joins the streams; the next read
+    of the streams does the write in its own pass, ``settle()`` does it alone.
     """
 
-    __slots__ = ("residual", "pending", "pending_norm", "extra", "_spare")
+    __slots__ = ("residual", "pending", "pending_norm", "extra", "_spare", "writer")
 
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None) -> None:
         self.residual = residual
@@ -42,15 +46,43 @@ class ResidualStream:
         self.pending_norm: Optional["Norm"] = None
         self.extra: Optional[torch.Tensor] = None
         self._spare: Optional[torch.Tensor] = None
+        self.writer = None
 
     @property
     def plain(self) -> bool:
         """True when what is outstanding is at most a plain delta (``pending``) to be added as it is."""
-        return self.pending_norm is None and self.extra is None
+        return self.pending_norm is None and self.extra is None and self.writer is None and self.residual.dim() == 2
+
+    def wanted_rows(self, indices: torch.Tensor) -> torch.Tensor:
+        """32-bit rows [len(indices), W] of the stream at the tokens ``indices`` with everything outstanding folded in
+        (for several streams per token: their sum).  The other tokens' rows are left as they are."""
+        from .. import kernels
+        rows = torch.empty((indices.numel(), self.residual.shape[-1]), dtype=torch.float32, device=indices.device)
+        if self.residual.dim() == 3:
+            write = self.writer.coefficients() if self.writer is not None else None
+            kernels.hyper_gather(self.residual, self.pending if write else None, write, indices, rows)
+            return rows
+        self.settle()
+        kernels.gather_rows(self.residual, self.pending, indices, rows)
+        return rows
+
+    def collapsed(self) -> torch.Tensor:
+        """The stream of every token as one 32-bit row [T, W], everything outstanding folded in."""
+        self.settle()
+        if self.residual.dim() == 3:
+            from .. import kernels
+            T, S, W = self.residual.shape
+            out = torch.empty((T, W), dtype=torch.float32, device=self.residual.device)
+            ones = torch.ones(S, dtype=torch.float32, device=self.residual.device)
+            kernels.hyper_stream(self.residual, None, None, ones, None, None, read_out=out)
+            return out
+        return self.residual + self.pending.float() if self.pending is not None else self.residual
 
     def settle(self) -> None:
         """Fold a normed delta and extra rows into the residual.  A plain pending delta stays pending: every norm and
         the gather of the wanted rows add it themselves."""
+        if self.writer is not None:
+            self.writer.fold(self)
         if self.pending_norm is not None:
             self.pending_norm.fold(self)
         if self.extra is not None:

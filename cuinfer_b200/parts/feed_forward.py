@@ -19,16 +19,26 @@ from .spec import PartSpec, TensorSpec
 
 
 @FEED_FORWARDS.register("swiglu")
+@FEED_FORWARDS.register("gated")
 class SwiGLU(FeedForward):
+    """``down( act(gate(x)) * up(x) )``.  Kind ``swiglu`` is the SiLU-gated form above; kind ``gated`` takes
+    ``activation`` (``"silu"`` or ``"gelu_tanh"``, the tanh form of GELU) and the tensors' names relative to the part's
+    prefix: ``PartSpec("gated", intermediate_size=I, activation="gelu_tanh", names=(gate, up, down))``."""
+
     accepts_lazy_norm = True       # the gate/up projection can compute the norm of its input itself
 
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.intermediate_size = int(spec.intermediate_size)
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation {self.activation!r} is not silu or gelu_tanh")
+        self._pair = True if self.activation == "silu" else self.activation        # what the projection's epilogue is told
+        gate, up, down = spec.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         p = prefix
-        self.gate_up = Linear([f"{p}.gate_proj.weight", f"{p}.up_proj.weight"],
+        self.gate_up = Linear([f"{p}.{gate}", f"{p}.{up}"],
                               [self.intermediate_size, self.intermediate_size], hidden_size, dtype)
-        self.down = Linear([f"{p}.down_proj.weight"], [hidden_size], self.intermediate_size, dtype)
+        self.down = Linear([f"{p}.{down}"], [hidden_size], self.intermediate_size, dtype)
 
     def tensors(self) -> List[TensorSpec]:
         return self.gate_up.tensors() + self.down.tensors()
@@ -48,7 +58,7 @@ class SwiGLU(FeedForward):
         return self.gate_up.workspace_bytes(tokens, silu_pair=True) + self.down.workspace_bytes(tokens)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        act = self.gate_up.forward(x, silu_pair=True)       # silu(gate) * up, fused where the kernel allows
+        act = self.gate_up.forward(x, silu_pair=self._pair)       # act(gate) * up, fused where the kernel allows
         return self.down.forward(act)
 
 

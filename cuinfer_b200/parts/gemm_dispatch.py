@@ -67,14 +67,15 @@ def takes_tcgen05(x: torch.Tensor, weight: torch.Tensor, fused: bool = False) ->
     return -(-M // 128) * -(-N // 128) >= TCGEN05_MIN_TILES
 
 
-def bf16_gated_matmul_nt(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor | None:
+def bf16_gated_matmul_nt(x: torch.Tensor, weight: torch.Tensor, gate=True) -> torch.Tensor | None:
     """silu(x gate^T) * (x up^T) for a weight of gate rows then up rows, in one tcgen05 kernel, when the shape is one
-    it takes (prompt-sized, half of N a multiple of 8); None otherwise."""
+    it takes (prompt-sized, half of N a multiple of 8); None otherwise.  ``gate="gelu_tanh"``: the tanh form of GELU in
+    the place of SiLU."""
     N = weight.shape[0]
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or N % 16 or not takes_tcgen05(x, weight, fused=True):
         return None
     out = torch.empty((x.shape[0], N // 2), dtype=torch.bfloat16, device=x.device)
-    kernels.gemm_tcgen05(x, weight, out, silu_pair=True)
+    kernels.gemm_tcgen05(x, weight, out, silu_pair=gate)
     return out
 
 

@@ -71,7 +71,7 @@ class Linear:
 
     def forward(self, x, out_dtype: Optional[torch.dtype] = None, silu_pair: bool = False) -> torch.Tensor:
         """``x`` is a tensor [M, K] or a :class:`LazyNorm`.  ``silu_pair``: the weight is gates then ups and the
-        result is ``silu(gate) * up`` [M, N/2]."""
+        result is ``silu(gate) * up`` [M, N/2]; the value ``"gelu_tanh"`` makes the gate the tanh form of GELU."""
         if self.weight is None:
             raise RuntimeError(f"projection {self.names} used before its weights were loaded")
         fused = self._forward_skinny(x, out_dtype, silu_pair)
@@ -81,14 +81,14 @@ class Linear:
             x = x.materialize()
         if silu_pair and x.dtype == torch.bfloat16 and x.shape[0] > 0:
             from . import gemm_dispatch
-            gated = gemm_dispatch.bf16_gated_matmul_nt(x, self.weight)
+            gated = gemm_dispatch.bf16_gated_matmul_nt(x, self.weight, silu_pair)
             if gated is not None:
                 return gated
         y = matmul_nt(x, self.weight, out_dtype if not silu_pair else None)
         if not silu_pair:
             return y
         act = torch.empty((y.shape[0], y.shape[1] // 2), dtype=y.dtype, device=y.device)
-        kernels.silu_mul(y, act)
+        kernels.silu_mul(y, act, gelu=silu_pair == "gelu_tanh")
         return act
 
     def _forward_skinny(self, x, out_dtype, silu_pair) -> Optional[torch.Tensor]:
@@ -113,7 +113,7 @@ class Linear:
         if choice == "wstream":
             # long K: the weight-streaming kernel (no norm prologue; the gate is in its epilogue)
             rows = x.materialize() if lazy else x
-            if (not silu_pair or rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or rows.stride(0) % 8 or w.stride(0) % 8
+            if (silu_pair is not True or rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or rows.stride(0) % 8 or w.stride(0) % 8
                     or not kernels.gemm_wstream_supports(M, N, K)):
                 return None
             out = torch.empty((M, out_cols), dtype=torch.bfloat16, device=w.device)

@@ -134,6 +134,8 @@ class DecoderModel:
         32-bit residual stream with its spare and a pending delta, the widest block's intermediate results, and the
         wanted rows with their logits (twice: the sampler works on a copy)."""
         residual = (4 if self.spec.reinject_embedding_before else 3) * tokens * self.hidden_size * 4
+        if self.spec.residual_streams:
+            residual = (self.spec.residual_streams + 1) * tokens * self.hidden_size * 4
         widest = max((block.workspace_bytes(tokens) for block in self.blocks), default=0)
         head = rows * (self.hidden_size * 8 + self.vocab_size * 8)
         return residual + widest + head
@@ -141,8 +143,10 @@ class DecoderModel:
     # ---- compute -------------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, tap=None) -> ResidualStream:
         """``tap(run, stream)``, if given, is called after every layer run with everything folded into the residual
-        (``stream.residual`` plus a plain ``stream.pending``, if any, is the stream after that run)."""
-        residual = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.token_ids.device)
+        (``stream.collapsed()`` is the stream after that run as one row per token)."""
+        streams = self.spec.residual_streams
+        shape = (ctx.num_tokens, streams, self.hidden_size) if streams else (ctx.num_tokens, self.hidden_size)
+        residual = torch.empty(shape, dtype=torch.float32, device=ctx.token_ids.device)
         kernels.embedding_gather(ctx.token_ids, self.embedding, residual, self._bad_id_flag, self.spec.embedding_scale)
         stream = ResidualStream(residual)
         # a model that feeds its embedding output in again keeps a copy: the residual rows are updated in place
@@ -161,9 +165,7 @@ class DecoderModel:
 
     def logits(self, stream: ResidualStream, indices: torch.Tensor) -> torch.Tensor:
         """32-bit logits ``[len(indices), vocab]`` of the rows ``indices`` of the step."""
-        stream.settle()
-        rows = torch.empty((indices.numel(), self.hidden_size), dtype=torch.float32, device=indices.device)
-        kernels.gather_rows(stream.residual, stream.pending, indices, rows)
+        rows = stream.wanted_rows(indices)
         normed = self.final_norm.norm_rows(rows)
         return self.lm_head.forward(normed, out_dtype=torch.float32)
 

@@ -1,7 +1,8 @@
 """RMSNorm: ``out = x · rsqrt(mean(x²) + eps) · w`` with the squares, the mean, the rsqrt and the product
 in 32 bits and one rounding at the end (csrc/ops/rms_norm.cu:43-71; eps inside the square root, the
-weight multiplies directly).  Spec: ``PartSpec("rmsnorm", eps=..., weight_suffix=".weight")``: the gain is the tensor
-``prefix + weight_suffix``.
+weight multiplies directly).  Spec: ``PartSpec("rmsnorm", eps=..., weight_suffix=".weight", one_plus=False)``: the gain is
+the tensor ``prefix + weight_suffix``, or, with ``one_plus``, one plus that tensor (a weight stored around zero; the sum
+is taken once at load, in 32 bits, and the gain stays 32-bit).
 
 The RMS norm also serves on a sub-layer's OUTPUT (a delta that is normed before it joins the residual): as
 ``stream.pending_norm`` it is folded by the next RMS norm of the stream in the same kernel, or alone by ``fold``.
@@ -23,14 +24,17 @@ class RMSNorm(Norm):
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.eps = float(spec.eps)
+        self.one_plus = bool(spec.get("one_plus", False))
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> List[TensorSpec]:
         return [TensorSpec(self.prefix + self.spec.get("weight_suffix", ".weight"), (self.hidden_size,),
-                           keep_stored_precision=True, init="ones")]
+                           keep_stored_precision=True, init="zeros" if self.one_plus else "ones")]
 
     def load(self, store) -> None:
         self.weight = store.get(self.tensors()[0])
+        if self.one_plus:
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def fusable_rms(self):
         return (self.weight, self.eps) if self.weight is not None else None

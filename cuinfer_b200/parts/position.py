@@ -88,6 +88,10 @@ class RotaryInterleaved(PositionEncoding):
         self._freq: Optional[torch.Tensor] = None
         self._device: Optional[torch.device] = None
 
+    # which elements form a pair: "interleaved" (2i, 2i+1) or "half" (i, i + rotary_dim / 2); the kernels that take the
+    # frequencies ask for it
+    layout = "interleaved"
+
     def host_frequencies(self) -> torch.Tensor:
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rotary_dim, 1))
@@ -113,3 +117,13 @@ class RotaryInterleaved(PositionEncoding):
                 _TABLES[key] = self.host_frequencies().to(device)
             self._freq = _TABLES[key]
         return self._freq
+
+
+@POSITION_ENCODINGS.register("rope_half")
+class RotaryHalf(RotaryInterleaved):
+    """The same rotation with another pairing: over the first ``rotary_dim`` elements, element i pairs with
+    ``i + rotary_dim / 2`` (i < rotary_dim / 2), angle ``p * theta ** (-2i / rotary_dim)``; the elements from
+    ``rotary_dim`` on pass unchanged.  No table and no largest position, as for ``rope_interleaved``, whose spec it
+    shares: ``PartSpec("rope_half", theta=..., rotary_dim=..., scaling=None)``."""
+
+    layout = "half"

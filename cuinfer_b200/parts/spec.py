@@ -100,6 +100,10 @@ class ModelSpec:
     # is added to the stream once more: a model that runs a span of layers several times feeds its input in again
     # at the start of every further pass
     reinject_embedding_before: tuple[int, ...] = ()
+    # 0: one residual row per token.  S >= 1: the residual is S rows per token ([T, S, W], all equal to the embedding
+    # output at the start) that the layers' blocks read from and write to with learned coefficients; the model's output
+    # is the sum of the rows
+    residual_streams: int = 0
 
     def run_order(self) -> tuple[int, ...]:
         order = self.order if self.order is not None else tuple(range(len(self.layers)))
@@ -130,7 +134,7 @@ class TensorSpec:
     shape: tuple[int, ...]
     keep_stored_precision: bool = False
     integer: bool = False    # an integer table (kept as int32); a floating tensor in its place is refused, and vice versa
-    init: str = "normal"     # how the random-weights mode fills it: "normal", "ones" (a gain), "zeros" (a bias)
+    init: str = "normal"     # how the random-weights mode fills it: "normal", "ones" (a gain), "zeros" (a bias), "identity" (a square matrix around one on its diagonal)
     modulus: int = 0         # for an integer table: entries are drawn from 0..modulus-1, different within a row
 
 
@@ -142,7 +146,9 @@ class PagedCacheNeed:
     next query can no longer see are given back).  ``planes``: how many rows of ``head_dim`` a head keeps per
     token — 2 for keys and values, 1 for a mixer that derives both from one cached row (a latent) or that keeps a
     token's key and value side by side in one row.  ``keep_first``: with a window, the first so many tokens of a request
-    stay visible (and their pages held) however far the window has moved.
+    stay visible (and their pages held) however far the window has moved.  ``chunked``: the window is a chunk — a query
+    at position i sees the keys from ``i // window * window`` on — so the pages before the chunk of a request's next
+    token are given back.
     """
 
     num_kv_heads: int
@@ -150,6 +156,7 @@ class PagedCacheNeed:
     window: int | None = None
     planes: int = 2
     keep_first: int = 0
+    chunked: bool = False
 
 
 @dataclass(frozen=True)

@@ -77,7 +77,7 @@ def integer_table(spec: TensorSpec, seed: int) -> torch.Tensor:
 
 def _draw_plan(spec: TensorSpec, std: float, gain_std: float, gains: Optional[Mapping[str, float]]):
     """(mean, std, factor) of a tensor: matrices N(0, std), gains 1 + N(0, gain_std), then the factors of ``gains``."""
-    mean, dev = (1.0, gain_std) if spec.init == "ones" else (0.0, gain_std) if spec.init == "zeros" else (0.0, std)
+    mean, dev = (1.0, gain_std) if spec.init == "ones" else (0.0, gain_std) if spec.init in ("zeros", "identity") else (0.0, std)
     factor = 1.0
     for pattern, f in (gains or {}).items():
         if pattern in spec.name:
@@ -111,11 +111,16 @@ def random_tensors(config: Mapping[str, Any], seed: int, *, std: float = 0.02, g
             mean, dev, factor = _draw_plan(spec, std, gain_std, gains)
             count = int(np.prod(spec.shape)) if spec.shape else 1
             t = counter_normal(_tensor_seed(seed, spec.name), count, mean, dev, factor, via_bf16=dtype == "bfloat16")
-            out[spec.name] = t.reshape(spec.shape).to(_TORCH_DTYPES[dtype])
+            t = t.reshape(spec.shape)
+            if spec.init == "identity":
+                t = t + torch.eye(spec.shape[0], dtype=torch.float32) * factor
+            out[spec.name] = t.to(_TORCH_DTYPES[dtype])
             continue
         gen = torch.Generator().manual_seed(_tensor_seed(seed, spec.name))
-        if spec.init in ("ones", "zeros"):
+        if spec.init in ("ones", "zeros", "identity"):
             t = torch.full(spec.shape, 1.0 if spec.init == "ones" else 0.0, dtype=torch.float32)
+            if spec.init == "identity":
+                t = torch.eye(spec.shape[0], dtype=torch.float32)
             if gain_std > 0:
                 t += torch.randn(spec.shape, generator=gen, dtype=torch.float32) * gain_std
         else:
@@ -198,6 +203,11 @@ class DeviceRandomStore:
         out = torch.empty(tuple(spec.shape), dtype=target, device=self.device)
         mean, dev, factor = _draw_plan(spec, self.std, self.gain_std, self.gains)
         kernels.fill_random(out, _tensor_seed(self.seed, spec.name), mean, dev, factor, via_bf16=self.stored == "bfloat16")
+        if spec.init == "identity":
+            out = out.float() + torch.eye(spec.shape[0], dtype=torch.float32, device=out.device) * factor
+            if self.stored == "bfloat16":
+                out = out.to(torch.bfloat16)          # as a file of bfloat16 tensors would hold it
+            out = out.to(target)
         return out
 
     def get_stacked(self, specs: Sequence[TensorSpec]) -> torch.Tensor:
