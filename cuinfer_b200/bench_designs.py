@@ -1,7 +1,8 @@
-"""Bilolorn and Kusolorn beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput through the
-model runner, and the time of every kernel of a step with the share of its roofline that it reaches.
+"""Bilolorn, Kusolorn and Desilorn beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput
+through the model runner, and the time of every kernel of a step with the share of its roofline that it reaches.
 
-``bench.py --designs`` runs this (``--design-names kusolorn,qwen3`` chooses the designs);
+``bench.py --designs`` runs this (``--design-names kusolorn,qwen3`` chooses the designs; ``kusolorn_attention`` is
+Kusolorn with windowed attention and a dense feed-forward in every layer, the closest model to Desilorn);
 ``python -m cuinfer_b200.bench_designs [--sizes small,large] [--designs kusolorn,qwen3]`` does the same.
 Weights are random, drawn on the device; the models have a few layers only (the figures are per step of that model;
 what is compared is one design against the other at the same sizes, and every kernel against its own roofline).
@@ -68,6 +69,30 @@ def kusolorn_config(s: dict) -> dict:
     layers = [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds * ((s["layers"] + 3) // 4))[:s["layers"]]]
     return {"architecture": "Kusolorn", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
             "token_side": {"dim": s["side_dim"]}, "layers": layers}
+
+
+def kusolorn_attention_config(s: dict) -> dict:
+    """Kusolorn with windowed attention and a dense feed-forward in every layer and no per-layer token input: the model
+    whose kernels are closest to Desilorn's, at the same sizes."""
+    attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["head_dim"], "vdim": s["head_dim"], "scale": s["head_dim"] ** -0.5,
+                 "softcap": 30.0, "v_mix": False, "mask": {"size": s["window"], "keep_first": s["keep_first"]},
+                 "rot": {"base": 1000000.0, "dims": s["head_dim"] // 2}}
+    layers = [{"type": "attention", "mixer": attention, "mlp": {"kind": "dense", "ff": s["ff"]}} for _ in range(s["layers"])]
+    return {"architecture": "Kusolorn", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def desilorn_config(s: dict) -> dict:
+    """Both kinds of attention in turn (the sliding window with its temperature, distance bias and learned sinks; chunks
+    with head norm and rotation in halves), the Qwen3 arm's head counts and head size, a dense feed-forward in every
+    layer, four residual streams, no looped span (every arm runs the same number of layers)."""
+    common = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["head_dim"], "vdim": s["head_dim"], "scale": s["head_dim"] ** -0.5,
+              "mask": {"size": s["window"]}}
+    sliding = dict(common, q_temp={"coef": 0.1, "every": 256})
+    chunks = dict(common, rot={"base": 1000000.0, "dims": s["head_dim"] // 2})
+    layers = [{"type": "attention" if i % 2 == 0 else "attention_2", "mixer": sliding if i % 2 == 0 else chunks,
+               "mlp": {"kind": "dense", "ff": s["ff"]}} for i in range(s["layers"])]
+    return {"architecture": "Desilorn", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "streams": s.get("streams", 4),
+            "layers": layers}
 
 
 def qwen3_config(s: dict) -> dict:
@@ -149,15 +174,20 @@ class KernelTimes:
         def rowwise(*a, **kw):
             return 0.0, _nbytes(*a, *kw.values())
 
-        def windowed(q, heads, qk, v, window, keep):
-            """Attention in which a query sees at most ``window`` keys and ``keep`` kept ones: FLOPs over the visible pairs,
-            bytes of the visible rows of the cache read once per request."""
+        def windowed(q, heads, qk, v, window, keep, chunked=False):
+            """Attention in which a query sees at most ``window`` keys and ``keep`` kept ones (with ``chunked`` the keys of
+            its own chunk of ``window`` positions): FLOPs over the visible pairs, bytes of the visible rows of the cache
+            read once per request."""
             pairs, rows = 0, 0
             for n, k in zip(lq, lk):
                 for p in range(k - n, k):
-                    pairs += min(p + 1, (window + keep) if window else p + 1)
-                rows += min(k, (window + keep + n) if window else k)
+                    pairs += (p % window + 1) if chunked and window else min(p + 1, (window + keep) if window else p + 1)
+                rows += min(k, k - (k - n) // window * window) if chunked and window else min(k, (window + keep + n) if window else k)
             return 2.0 * pairs * heads * (qk + v), rows * (qk + v) * 2 + q.shape[0] * heads * (qk + v) * 2
+
+        def hyper(streams, y, write, read, norm, out, read_out=None):
+            """One pass over the streams: read once, written once when a sub-layer's output is outstanding."""
+            return 0.0, _nbytes(streams) * (2 if y is not None else 1) + _nbytes(y, out, read_out)
 
         def scan(tokens, heads, d, dv, per_pair, state):
             """A recurrence over a matrix per head: ``per_pair`` operations per token and matrix element; the state is read
@@ -165,12 +195,13 @@ class KernelTimes:
             return float(per_pair) * tokens * heads * d * dv, 2 * _nbytes(state) * len(lq) / max(1, state.shape[0]) + tokens * heads * (2 * d + 2 * dv) * 4
 
         costs = {
-            "rms_stream": rowwise, "gelu_tanh": rowwise, "router_topk": rowwise, "head_rms_gate": rowwise,
+            "rms_stream": rowwise, "hyper_stream": hyper, "hyper_gather": lambda st, y, w, idx, out: (0.0, (st.shape[1] + 1) * _nbytes(out)),
+            "gelu_tanh": rowwise, "router_topk": rowwise, "head_rms_gate": rowwise,
             "window_attention_prep": lambda qkv, *a, **k: (0.0, 2 * _nbytes(qkv)),
-            "window_attention_generic": lambda q, out, cache, bt, pos, tr, H, G, d, dv, scale, cap, window, keep:
-                windowed(q, H, d, dv, window, keep),
+            "window_attention_generic": lambda q, out, cache, bt, pos, tr, H, G, d, dv, scale, cap, window, keep, **kw:
+                windowed(q, H, d, dv, window, keep, kw.get("chunked", False)),
             "window_attention_mma": lambda q, out, cache, bt, qsl, sl, ql, H, G, d, dv, scale, cap, window, keep, **kw:
-                windowed(q, H, d, dv, window, keep),
+                windowed(q, H, d, dv, window, keep, kw.get("chunked", False)),
             "mlstm_scan": lambda q, k, v, gates, ib, fb, cap, qs, state, qsl, slots, out, H, d, dv, **kw: scan(out.shape[0], H, d, dv, 4, state),
             "delta_scan": lambda qkv, gates, al, db, state, qsl, slots, out, G, H, d, dv: scan(out.shape[0], H, d, dv, 6, state),
             "delta_prep": lambda x, taps, cs, qsl, tr, slots, G, H, d, dv, ue, qs, out: (0.0, _nbytes(out) + out.numel() * x.element_size()),
@@ -227,7 +258,8 @@ def measure(design: str, size: str, prefill_tokens: int, batch: int, context: in
     from .engine.runner import StepEntry
 
     s = SIZES[size]
-    config = {"bilolorn": bilolorn_config, "kusolorn": kusolorn_config, "qwen3": qwen3_config}[design](s)
+    config = {"bilolorn": bilolorn_config, "kusolorn": kusolorn_config, "kusolorn_attention": kusolorn_attention_config,
+              "desilorn": desilorn_config, "qwen3": qwen3_config}[design](s)
     pages = (batch * (context + steps + 64) + prefill_tokens) // 16 + 64
     runner = make_runner(config, pages, max_seqs=max(batch, 8), graphs=True)
     gen = torch.Generator().manual_seed(5)

@@ -152,26 +152,106 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, taps: Option
     """Logits [T, vocab] of one sequence fed whole.  ``taps``: a list that gets the sum of the streams after every
     layer run."""
     eps = float(config["norm"]["eps"])
-    S = int(config.get("streams", 1))
+    S = int(config.get("streams", 0))              # 0: one residual row and a plain sum
     x = weights["embed"][torch.as_tensor(tokens, dtype=torch.long)]
-    xs = torch.stack([x] * S)
+    xs = torch.stack([x] * max(S, 1))
+
+    def sublayer(xs, p, q, fn):
+        if not S:
+            return xs + fn(norm_one_plus(xs[0], weights[p + f"norm{q}"], eps))[None]
+        u = streams_read(xs, weights[p + f"hc{q}.in"])
+        y = fn(norm_one_plus(u, weights[p + f"norm{q}"], eps))
+        return streams_write(xs, y, weights[p + f"hc{q}.mix"], weights[p + f"hc{q}.out"])
+
     for i in run_order(config):
         layer = config["layers"][i]
         p = f"l{i}."
-        u = streams_read(xs, weights[p + "hc1.in"])
-        hnorm = norm_one_plus(u, weights[p + "norm1"], eps)
         if layer["type"] == "attention":
-            y = attention_sliding(hnorm, sub(weights, p + "mix."), layer["mixer"])
+            xs = sublayer(xs, p, 1, lambda h: attention_sliding(h, sub(weights, p + "mix."), layer["mixer"]))
         elif layer["type"] == "attention_2":
-            y = attention_chunked(hnorm, sub(weights, p + "mix."), layer["mixer"], eps)
+            xs = sublayer(xs, p, 1, lambda h: attention_chunked(h, sub(weights, p + "mix."), layer["mixer"], eps))
         else:
             raise ValueError(layer["type"])
-        xs = streams_write(xs, y, weights[p + "hc1.mix"], weights[p + "hc1.out"])
         if layer.get("mlp"):
-            u = streams_read(xs, weights[p + "hc2.in"])
-            y = feed_forward(norm_one_plus(u, weights[p + "norm2"], eps), sub(weights, p + "mlp."))
-            xs = streams_write(xs, y, weights[p + "hc2.mix"], weights[p + "hc2.out"])
+            xs = sublayer(xs, p, 2, lambda h: feed_forward(h, sub(weights, p + "mlp.")))
         if taps is not None:
             taps.append(xs.sum(0))
     x = norm_one_plus(xs.sum(0), weights["final.norm"], eps)
     return x @ weights["embed"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt, steps: int) -> List[int]:
+    """Greedy continuation, recomputing the whole sequence every step (the lower id wins a tie)."""
+    toks = list(prompt)
+    out = []
+    for _ in range(steps):
+        nxt = int(torch.argmax(forward(config, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+# ---- random weights for the tests ------------------------------------------------------------------------------------
+def tensor_shapes(config: dict) -> Dict[str, tuple]:
+    """Name -> shape of every tensor a model of this configuration has."""
+    W, V, S = config["width"], config["vocab"], int(config.get("streams", 0))
+    out: Dict[str, tuple] = {"embed": (V, W), "final.norm": (W,)}
+    for i, layer in enumerate(config["layers"]):
+        m = layer["mixer"]
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        p = f"l{i}."
+        out[p + "norm1"] = (W,)
+        for name, rows in (("q", H * d), ("k", G * d), ("v", G * dv)):
+            out[p + f"mix.{name}"] = (rows, W)
+            out[p + f"mix.{name}.b"] = (rows,)
+        out[p + "mix.o"] = (W, H * dv)
+        if layer["type"] == "attention":
+            out[p + "mix.sink"] = (H,)
+        else:
+            out[p + "mix.q.norm"] = (d,)
+            out[p + "mix.k.norm"] = (d,)
+        subs = ["hc1"]
+        if layer.get("mlp"):
+            ff = layer["mlp"]["ff"]
+            out[p + "norm2"] = (W,)
+            out[p + "mlp.gate"] = (ff, W)
+            out[p + "mlp.up"] = (ff, W)
+            out[p + "mlp.down"] = (W, ff)
+            subs.append("hc2")
+        if S:
+            for q in subs:
+                out[p + f"{q}.in"] = (S,)
+                out[p + f"{q}.out"] = (S,)
+                out[p + f"{q}.mix"] = (S, S)
+    return out
+
+
+def random_model(config: dict, seed: int, sharp: float = 2.5, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Weights whose values are bfloat16 numbers.  ``sharp`` scales the query projections, so that the scores spread out
+    and a wrong, missing or stale key moves the logits."""
+    g = torch.Generator().manual_seed(seed)
+    t: Dict[str, torch.Tensor] = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.split(".", 1)[1] if name.startswith("l") and "." in name else name
+        if len(shape) == 2 and not leaf.endswith(".mix") or leaf in ("mix.o",):
+            x = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+            if leaf == "mix.q":
+                x = x * sharp
+            if name == "embed":
+                x = torch.randn(shape, generator=g)
+        elif leaf.endswith(".mix") and len(shape) == 2:              # stream to stream: around the identity
+            x = torch.eye(shape[0]) + 0.25 * torch.randn(shape, generator=g)
+        elif leaf.endswith(".in"):
+            x = 1.0 / shape[0] + 0.3 * torch.randn(shape, generator=g)
+        elif leaf.endswith(".out"):
+            x = 1.0 + 0.4 * torch.randn(shape, generator=g)
+        elif leaf in ("mix.q.norm", "mix.k.norm"):
+            x = 1.0 + 0.3 * torch.randn(shape, generator=g)
+        elif leaf == "mix.sink":
+            x = 1.5 * torch.randn(shape, generator=g)
+        elif leaf.endswith(".b"):
+            x = 0.3 * torch.randn(shape, generator=g)
+        else:                                                        # norm weights, stored around zero
+            x = 0.2 * torch.randn(shape, generator=g)
+        t[name] = x.bfloat16().to(dtype)
+    return t
