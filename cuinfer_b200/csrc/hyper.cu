@@ -4,8 +4,9 @@
 //   (1) the write of the sub-layer before (y, mix, out), in place;
 //   (2) the read of the next sub-layer (in) and its RMS norm, u * rsqrt(mean(u^2) + eps) * gain, rounded once;
 //   (3) u itself as a 32-bit row.
-// Everything is 32-bit: coefficients, sums, the norm.  A block per token; a column's S values live in registers, the
-// row u in shared memory between the two passes of the norm.
+// Everything is 32-bit: coefficients, sums, the norm.  A block per token; a thread takes four neighbouring columns at a
+// time (one where W is no multiple of four or there are more than eight streams), whose S values live in registers; the
+// row u waits in shared memory between the two passes of the norm.
 //
 // hyper_gather: for a few wanted tokens only, the sum of the streams after an outstanding write,
 //   sum_t x_t' = sum_s (sum_t mix[s][t]) x_s + (sum_t out[t]) y, without touching the other tokens' rows.
@@ -13,114 +14,210 @@
 
 namespace cib {
 
-constexpr int kHyperMaxStreams = 8;
+constexpr int kHyperMaxStreams = 16;
 
-template <typename TY, typename TO, int SM>
-__global__ void __launch_bounds__(256)
+// V consecutive columns of a row as one access (V = 1 or 4; with 4 the row starts on 16 bytes and W is a multiple of 4).
+template <int V>
+__device__ __forceinline__ void load_f32(const float* p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+        v[0] = *p;
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_f32(float* p, const float (&v)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else *p = v[0];
+}
+template <int V>
+__device__ __forceinline__ void load_any(const float* p, float (&v)[V]) { load_f32<V>(p, v); }
+template <int V>
+__device__ __forceinline__ void load_any(const __nv_bfloat16* p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+        v[0] = __bfloat162float(*p);
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_any(float* p, const float (&v)[V]) { store_f32<V>(p, v); }
+template <int V>
+__device__ __forceinline__ void store_any(__nv_bfloat16* p, const float (&v)[V]) {
+    if constexpr (V == 4) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a);
+        raw.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    } else {
+        *p = __float2bfloat16_rn(v[0]);
+    }
+}
+
+// The largest block of hyper_stream_kernel<.., SM, V>: 2 * SM * V values of a thread's columns live in registers.
+constexpr int hyper_block_cap(int SM, int V) { return SM * V > 16 || SM > 8 ? 256 : 512; }
+
+template <typename TY, typename TO, int SM, int V>
+__global__ void __launch_bounds__(hyper_block_cap(SM, V))
 hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ mix,
                     const float* __restrict__ out_w, const float* __restrict__ in_w, AnyVec gain, int has_gain, float eps,
                     TO* __restrict__ normed, float* __restrict__ read_out, int S, int W) {
-    extern __shared__ float u_row[];
+    extern __shared__ __align__(16) float u_row[];
     __shared__ float scratch[33];
     __shared__ float s_mix[kHyperMaxStreams * kHyperMaxStreams], s_out[kHyperMaxStreams], s_in[kHyperMaxStreams];
     const int t = blockIdx.x;
-    if (threadIdx.x < S * S) s_mix[threadIdx.x] = y ? mix[threadIdx.x] : 0.f;
-    if (threadIdx.x < S) {
-        s_out[threadIdx.x] = y ? out_w[threadIdx.x] : 0.f;
-        s_in[threadIdx.x] = in_w ? in_w[threadIdx.x] : 0.f;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = y ? mix[i] : 0.f;
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        s_out[i] = y ? out_w[i] : 0.f;
+        s_in[i] = in_w ? in_w[i] : 0.f;
     }
     __syncthreads();
     float* rows = x + (size_t)t * S * W;
     const bool reads = in_w != nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float old[SM], cur[SM];
+    for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+        float old[SM][V], cur[SM][V];
 #pragma unroll
-        for (int s = 0; s < SM; ++s) old[s] = s < S ? rows[(size_t)s * W + i] : 0.f;
+        for (int s = 0; s < SM; ++s) {
+            if (s < S) {
+                load_f32<V>(rows + (size_t)s * W + i, old[s]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < V; ++c) old[s][c] = 0.f;
+            }
+        }
         if (y) {
-            const float yv = to_f32(y[(size_t)t * W + i]);
+            float yv[V];
+            load_any<V>(y + (size_t)t * W + i, yv);
 #pragma unroll
             for (int d = 0; d < SM; ++d) {
                 if (d < S) {
-                    float acc = 0.f;
 #pragma unroll
-                    for (int s = 0; s < SM; ++s)
-                        if (s < S) acc = fmaf(s_mix[s * S + d], old[s], acc);
-                    cur[d] = fmaf(s_out[d], yv, acc);
-                    rows[(size_t)d * W + i] = cur[d];
+                    for (int c = 0; c < V; ++c) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int s = 0; s < SM; ++s)
+                            if (s < S) acc = fmaf(s_mix[s * S + d], old[s][c], acc);
+                        cur[d][c] = fmaf(s_out[d], yv[c], acc);
+                    }
+                    store_f32<V>(rows + (size_t)d * W + i, cur[d]);
                 }
             }
         } else {
 #pragma unroll
-            for (int s = 0; s < SM; ++s) cur[s] = old[s];
+            for (int s = 0; s < SM; ++s)
+#pragma unroll
+                for (int c = 0; c < V; ++c) cur[s][c] = old[s][c];
         }
         if (reads) {
-            float u = 0.f;
+            float u[V];
 #pragma unroll
-            for (int s = 0; s < SM; ++s)
-                if (s < S) u = fmaf(s_in[s], cur[s], u);
-            if (read_out) read_out[(size_t)t * W + i] = u;
+            for (int c = 0; c < V; ++c) {
+                u[c] = 0.f;
+#pragma unroll
+                for (int s = 0; s < SM; ++s)
+                    if (s < S) u[c] = fmaf(s_in[s], cur[s][c], u[c]);
+            }
+            if (read_out) store_f32<V>(read_out + (size_t)t * W + i, u);
             if (normed) {
-                u_row[i] = u;
-                ss += u * u;
+                store_f32<V>(u_row + i, u);
+#pragma unroll
+                for (int c = 0; c < V; ++c) ss = fmaf(u[c], u[c], ss);
             }
         }
     }
     if (!reads || !normed) return;
     ss = block_sum(ss, scratch);
     const float factor = 1.f / sqrtf(ss / (float)W + eps);
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float g = has_gain ? gain[i] : 1.f;
-        normed[(size_t)t * W + i] = from_f32<TO>(u_row[i] * factor * g);
+    for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+        float u[V];
+        load_f32<V>(u_row + i, u);
+#pragma unroll
+        for (int c = 0; c < V; ++c) u[c] = u[c] * factor * (has_gain ? gain[i + c] : 1.f);
+        store_any<V>(normed + (size_t)t * W + i, u);
     }
 }
 
-template <typename TY>
-__global__ void hyper_gather_kernel(const float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ mix,
-                                    const float* __restrict__ out_w, const int* __restrict__ indices, float* __restrict__ out,
-                                    int S, int W, int num_tokens) {
+template <typename TY, int V>
+__global__ void __launch_bounds__(512)
+hyper_gather_kernel(const float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ mix,
+                    const float* __restrict__ out_w, const int* __restrict__ indices, float* __restrict__ out,
+                    int S, int W, int num_tokens) {
     __shared__ float c[kHyperMaxStreams + 1];
-    if (threadIdx.x <= S) {
+    for (int j = threadIdx.x; j <= S; j += blockDim.x) {
         float v = 1.f;
         if (y) {
             v = 0.f;
-            for (int d = 0; d < S; ++d) v += threadIdx.x < S ? mix[threadIdx.x * S + d] : out_w[d];
-        } else if (threadIdx.x == S) {
+            for (int d = 0; d < S; ++d) v += j < S ? mix[j * S + d] : out_w[d];
+        } else if (j == S) {
             v = 0.f;
         }
-        c[threadIdx.x] = v;
+        c[j] = v;
     }
     __syncthreads();
     const int t = indices[blockIdx.x];
-    if (t < 0 || t >= num_tokens) {
-        for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)blockIdx.x * W + i] = 0.f;
-        return;
+    const bool outside = t < 0 || t >= num_tokens;
+    const float* rows = x + (size_t)(outside ? 0 : t) * S * W;
+    for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = 0.f;
+        if (!outside) {
+            if (y) {
+                float yv[V];
+                load_any<V>(y + (size_t)t * W + i, yv);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = c[S] * yv[k];
+            }
+            for (int s = 0; s < S; ++s) {
+                float v[V];
+                load_f32<V>(rows + (size_t)s * W + i, v);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = fmaf(c[s], v[k], acc[k]);
+            }
+        }
+        store_f32<V>(out + (size_t)blockIdx.x * W + i, acc);
     }
-    const float* rows = x + (size_t)t * S * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float acc = y ? c[S] * to_f32(y[(size_t)t * W + i]) : 0.f;
-        for (int s = 0; s < S; ++s) acc = fmaf(c[s], rows[(size_t)s * W + i], acc);
-        out[(size_t)blockIdx.x * W + i] = acc;
-    }
+}
+
+// Threads for rows of W values taken V at a time: a multiple of 32 between 64 and `cap`.
+static int hyper_threads(int W, int V, int cap = 512) {
+    const int n = ((W + V - 1) / V + 31) / 32 * 32;
+    return n < 64 ? 64 : n > cap ? cap : n;
 }
 
 template <typename TY, typename TO>
 static int launch_hyper_stream(float* x, const void* y, const float* mix, const float* out_w, const float* in_w, AnyVec gain,
                                int has_gain, float eps, void* normed, float* read_out, int S, int W, int T, cudaStream_t stream) {
-    const int threads = W >= 256 ? 256 : ((W + 31) / 32 * 32 < 64 ? 64 : (W + 31) / 32 * 32);
+    // four columns per access where every row starts on 16 bytes; beyond eight streams a column's values alone fill the
+    // registers
+    const bool wide = W % 4 == 0 && S <= 8;
     const size_t smem = normed ? (size_t)W * sizeof(float) : 0;
-#define CIB_HS(SMv)                                                                                                             \
-    {                                                                                                                           \
-        static SmemLimit limit;                                                                                                 \
-        if (smem > 48 * 1024)                                                                                                   \
-            if (int rc = raise_smem_limit(limit, hyper_stream_kernel<TY, TO, SMv>, 200 * 1024, "hyper_stream")) return rc;      \
-        hyper_stream_kernel<TY, TO, SMv><<<T, threads, smem, stream>>>(x, (const TY*)y, mix, out_w, in_w, gain, has_gain, eps, \
-                                                                       (TO*)normed, read_out, S, W);                            \
+#define CIB_HS(SMv, Vv)                                                                                                          \
+    {                                                                                                                            \
+        static SmemLimit limit;                                                                                                  \
+        if (smem > 48 * 1024)                                                                                                    \
+            if (int rc = raise_smem_limit(limit, hyper_stream_kernel<TY, TO, SMv, Vv>, 200 * 1024, "hyper_stream")) return rc;   \
+        hyper_stream_kernel<TY, TO, SMv, Vv><<<T, hyper_threads(W, Vv, hyper_block_cap(SMv, Vv)), smem, stream>>>(x, (const TY*)y, mix, out_w, in_w, gain, has_gain,   \
+                                                                           eps, (TO*)normed, read_out, S, W);                    \
     }
-    if (S == 1) CIB_HS(1)
-    else if (S == 2) CIB_HS(2)
-    else if (S <= 4) CIB_HS(4)
-    else CIB_HS(8)
+    if (wide) {
+        if (S == 1) CIB_HS(1, 4)
+        else if (S == 2) CIB_HS(2, 4)
+        else if (S <= 4) CIB_HS(4, 4)
+        else CIB_HS(8, 4)
+    } else {
+        if (S == 1) CIB_HS(1, 1)
+        else if (S == 2) CIB_HS(2, 1)
+        else if (S <= 4) CIB_HS(4, 1)
+        else if (S <= 8) CIB_HS(8, 1)
+        else CIB_HS(16, 1)
+    }
 #undef CIB_HS
     return 0;
 }
@@ -161,13 +258,17 @@ extern "C" int cib_hyper_gather(const float* x, const void* y, int y_dtype, cons
     CIB_REQUIRE(S >= 1 && S <= kHyperMaxStreams && W > 0 && T >= 0 && rows >= 0, "hyper_gather: bad sizes");
     CIB_REQUIRE(y == nullptr || (mix && out_w), "hyper_gather: a write needs its coefficients");
     if (rows == 0) return 0;
-    const int threads = W >= 256 ? 256 : 64;
-    if (y == nullptr || y_dtype == kF32)
-        hyper_gather_kernel<float><<<rows, threads, 0, stream>>>(x, (const float*)y, mix, out_w, indices, out, S, W, T);
-    else if (y_dtype == kBF16)
-        hyper_gather_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)y, mix, out_w, indices, out, S, W, T);
-    else
+    const bool wide = W % 4 == 0;
+    const int threads = hyper_threads(W, wide ? 4 : 1);
+    if (y == nullptr || y_dtype == kF32) {
+        if (wide) hyper_gather_kernel<float, 4><<<rows, threads, 0, stream>>>(x, (const float*)y, mix, out_w, indices, out, S, W, T);
+        else hyper_gather_kernel<float, 1><<<rows, threads, 0, stream>>>(x, (const float*)y, mix, out_w, indices, out, S, W, T);
+    } else if (y_dtype == kBF16) {
+        if (wide) hyper_gather_kernel<__nv_bfloat16, 4><<<rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)y, mix, out_w, indices, out, S, W, T);
+        else hyper_gather_kernel<__nv_bfloat16, 1><<<rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)y, mix, out_w, indices, out, S, W, T);
+    } else {
         CIB_REQUIRE(false, "hyper_gather: bad dtype %d", y_dtype);
+    }
     CIB_LAUNCH_CHECK("hyper_gather");
     return 0;
 }

@@ -38,7 +38,7 @@ MAX_POSITIONS = 1 << 17
 MIXER_TYPES = ("attention", "attention_2")
 # The distance bias of head h is 2 ** (-DISTANCE_BIAS_EXPONENT * (h + 1) / heads) per token of distance.
 DISTANCE_BIAS_EXPONENT = 8.0
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 def _obj(raw: Mapping[str, Any], key: str, where: str, optional: bool = False) -> Optional[Mapping[str, Any]]:

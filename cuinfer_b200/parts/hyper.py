@@ -33,8 +33,8 @@ class HyperConnection(Part):
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.streams = int(spec.streams)
-        if not 1 <= self.streams <= 8:
-            raise ValueError(f"hyper-connections: {self.streams} streams are beyond what the kernel takes (1 to 8)")
+        if not 1 <= self.streams <= 16:
+            raise ValueError(f"hyper-connections: {self.streams} streams are beyond what the kernel takes (1 to 16)")
         self.names = tuple(spec.get("coefficient_names", ("in", "out", "mix")))
         self.read_w: Optional[torch.Tensor] = None
         self.out_w: Optional[torch.Tensor] = None

@@ -300,7 +300,7 @@ class _Store:
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,W", [(1, 40), (2, 64), (3, 37), (4, 256), (5, 1000), (8, 72)])
+@pytest.mark.parametrize("S,W", [(1, 40), (2, 64), (3, 37), (4, 256), (5, 1000), (8, 72), (4, 4096), (7, 2052), (12, 48), (16, 33)])
 def test_streams_are_read_and_written_in_one_pass(dtype, S, W):
     """Write alone, read with its norm alone, both in one pass, and the read row itself; the streams stay 32-bit."""
     from cuinfer_b200 import kernels
