@@ -4,8 +4,8 @@
 //   (1) the write of the sub-layer before (y, mix, out), in place;
 //   (2) the read of the next sub-layer (in) and its RMS norm, u * rsqrt(mean(u^2) + eps) * gain, rounded once;
 //   (3) u itself as a 32-bit row.
-// Everything is 32-bit: coefficients, sums, the norm.  A block per token; a thread takes four neighbouring columns at a
-// time (one where W is no multiple of four or there are more than eight streams), whose S values live in registers; the
+// Everything is 32-bit: coefficients, sums, the norm.  A block per token; a thread takes four, two or one neighbouring columns at a
+// time (as W and the number of streams allow), whose S values live in registers; the
 // row u waits in shared memory between the two passes of the norm.
 //
 // hyper_gather: for a few wanted tokens only, the sum of the streams after an outstanding write,
@@ -16,12 +16,15 @@ namespace cib {
 
 constexpr int kHyperMaxStreams = 16;
 
-// V consecutive columns of a row as one access (V = 1 or 4; with 4 the row starts on 16 bytes and W is a multiple of 4).
+// V consecutive columns of a row as one access (V = 1, 2 or 4; the row starts on 4 V bytes and W is a multiple of V).
 template <int V>
 __device__ __forceinline__ void load_f32(const float* p, float (&v)[V]) {
     if constexpr (V == 4) {
         const float4 t = *reinterpret_cast<const float4*>(p);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else if constexpr (V == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        v[0] = t.x; v[1] = t.y;
     } else {
         v[0] = *p;
     }
@@ -29,6 +32,7 @@ __device__ __forceinline__ void load_f32(const float* p, float (&v)[V]) {
 template <int V>
 __device__ __forceinline__ void store_f32(float* p, const float (&v)[V]) {
     if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else if constexpr (V == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
     else *p = v[0];
 }
 template <int V>
@@ -40,6 +44,9 @@ __device__ __forceinline__ void load_any(const __nv_bfloat16* p, float (&v)[V]) 
         const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
         const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
         v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else if constexpr (V == 2) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+        v[0] = a.x; v[1] = a.y;
     } else {
         v[0] = __bfloat162float(*p);
     }
@@ -54,6 +61,8 @@ __device__ __forceinline__ void store_any(__nv_bfloat16* p, const float (&v)[V])
         raw.x = *reinterpret_cast<const unsigned*>(&a);
         raw.y = *reinterpret_cast<const unsigned*>(&b);
         *reinterpret_cast<uint2*>(p) = raw;
+    } else if constexpr (V == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
     } else {
         *p = __float2bfloat16_rn(v[0]);
     }
@@ -63,7 +72,7 @@ __device__ __forceinline__ void store_any(__nv_bfloat16* p, const float (&v)[V])
 constexpr int hyper_block_cap(int SM, int V) { return SM * V > 16 || SM > 8 ? 256 : 512; }
 
 template <typename TY, typename TO, int SM, int V>
-__global__ void __launch_bounds__(hyper_block_cap(SM, V))
+__global__ void __launch_bounds__(hyper_block_cap(SM, V), hyper_block_cap(SM, V) == 512 ? 2 : 1)
 hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ mix,
                     const float* __restrict__ out_w, const float* __restrict__ in_w, AnyVec gain, int has_gain, float eps,
                     TO* __restrict__ normed, float* __restrict__ read_out, int S, int W) {
@@ -194,23 +203,31 @@ static int hyper_threads(int W, int V, int cap = 512) {
 template <typename TY, typename TO>
 static int launch_hyper_stream(float* x, const void* y, const float* mix, const float* out_w, const float* in_w, AnyVec gain,
                                int has_gain, float eps, void* normed, float* read_out, int S, int W, int T, cudaStream_t stream) {
-    // four columns per access where every row starts on 16 bytes; beyond eight streams a column's values alone fill the
-    // registers
-    const bool wide = W % 4 == 0 && S <= 8;
+    // sixteen values of a thread's columns at most (four streams of four columns, eight of two), so that two blocks of 512
+    // threads share an SM; the widest access that W allows
+    const int V = S <= 4 && W % 4 == 0 ? 4 : S <= 8 && W % 2 == 0 ? 2 : 1;
     const size_t smem = normed ? (size_t)W * sizeof(float) : 0;
+    // Few tokens (decode steps): the largest block, so that a row is done in the fewest dependent rounds of loads.  Many:
+    // blocks of 256, of which the registers let three or more share an SM (measured at 8 192 tokens of 4 x 4 096:
+    // one block of 512 threads per SM, 25 % of the warp slots, 3.7 TB/s).
+    const bool many = T >= 2 * 148;
 #define CIB_HS(SMv, Vv)                                                                                                          \
     {                                                                                                                            \
         static SmemLimit limit;                                                                                                  \
         if (smem > 48 * 1024)                                                                                                    \
             if (int rc = raise_smem_limit(limit, hyper_stream_kernel<TY, TO, SMv, Vv>, 200 * 1024, "hyper_stream")) return rc;   \
-        hyper_stream_kernel<TY, TO, SMv, Vv><<<T, hyper_threads(W, Vv, hyper_block_cap(SMv, Vv)), smem, stream>>>(x, (const TY*)y, mix, out_w, in_w, gain, has_gain,   \
+        hyper_stream_kernel<TY, TO, SMv, Vv><<<T, hyper_threads(W, Vv, many ? 256 : hyper_block_cap(SMv, Vv)), smem, stream>>>(x, (const TY*)y, mix, out_w, in_w, gain, has_gain,   \
                                                                            eps, (TO*)normed, read_out, S, W);                    \
     }
-    if (wide) {
+    if (V == 4) {
         if (S == 1) CIB_HS(1, 4)
         else if (S == 2) CIB_HS(2, 4)
-        else if (S <= 4) CIB_HS(4, 4)
-        else CIB_HS(8, 4)
+        else CIB_HS(4, 4)
+    } else if (V == 2) {
+        if (S == 1) CIB_HS(1, 2)
+        else if (S == 2) CIB_HS(2, 2)
+        else if (S <= 4) CIB_HS(4, 2)
+        else CIB_HS(8, 2)
     } else {
         if (S == 1) CIB_HS(1, 1)
         else if (S == 2) CIB_HS(2, 1)
