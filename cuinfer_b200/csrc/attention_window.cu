@@ -39,8 +39,9 @@ struct PrepOptions {
     int temp_every;
 };
 
-// One warp per (token, vector): H query heads, G key heads, G value heads of the packed rows [q | k | v].
-template <typename T>
+// One warp per (token, vector): H query heads, G key heads, G value heads of the packed rows [q | k | v].  C: pairs of
+// values a lane holds (d <= 64 C).
+template <typename T, int C>
 __global__ void __launch_bounds__(kPrepWarps * 32)
 window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restrict__ positions,
                              const int* __restrict__ slot_mapping, const float* __restrict__ freq, int rot_dims, float eps,
@@ -79,12 +80,12 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
     const int ipos = positions[t];
     const float pos = (float)ipos;
     const int half = rot_dims / 2;
-    float a[kPrepMaxPairsPerLane], b[kPrepMaxPairsPerLane];
+    float a[C], b[C];
     // pair p of the lane's pairs: the rotation partners, or two neighbours of the part that is not rotated
     auto first_of = [&](int p) { return opt.rot_half && p < half ? p : 2 * p; };
     auto second_of = [&](int p) { return opt.rot_half && p < half ? p + half : 2 * p + 1; };
 #pragma unroll
-    for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+    for (int c = 0; c < C; ++c) {
         const int p = c * 32 + lane, e0 = first_of(p), e1 = second_of(p);
         a[c] = e0 < d ? to_f32(x[e0]) + (bias ? bias[e0] : 0.f) : 0.f;
         b[c] = e1 < d ? to_f32(x[e1]) + (bias ? bias[e1] : 0.f) : 0.f;
@@ -92,11 +93,11 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
     auto normalise = [&]() {
         float ss = 0.f;
 #pragma unroll
-        for (int c = 0; c < kPrepMaxPairsPerLane; ++c) ss += a[c] * a[c] + b[c] * b[c];
+        for (int c = 0; c < C; ++c) ss += a[c] * a[c] + b[c] * b[c];
         ss = warp_sum(ss);
         const float factor = 1.f / sqrtf(ss / (float)d + eps);
 #pragma unroll
-        for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+        for (int c = 0; c < C; ++c) {
             const int p = c * 32 + lane, e0 = first_of(p), e1 = second_of(p);
             a[c] *= factor * (gain && e0 < d ? gain[e0] : 1.f);
             b[c] *= factor * (gain && e1 < d ? gain[e1] : 1.f);
@@ -104,7 +105,7 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
     };
     if (opt.norm && opt.norm_first) normalise();
 #pragma unroll
-    for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+    for (int c = 0; c < C; ++c) {
         const int p = c * 32 + lane;
         if (p < half && second_of(p) < d) {
             float sn, cs;
@@ -118,7 +119,7 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
     if (opt.has_temp && !is_key) {
         const float temp = 1.f + opt.temp_coef * logf((float)((ipos + 1) / opt.temp_every + 1));
 #pragma unroll
-        for (int c = 0; c < kPrepMaxPairsPerLane; ++c) { a[c] *= temp; b[c] *= temp; }
+        for (int c = 0; c < C; ++c) { a[c] *= temp; b[c] *= temp; }
     }
     T* dst = x;
     if (is_key) {
@@ -126,7 +127,7 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
         dst = cache + (((size_t)(slot / page_size) * G + (vec - H)) * page_size + slot % page_size) * width;
     }
 #pragma unroll
-    for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+    for (int c = 0; c < C; ++c) {
         const int p = c * 32 + lane, e0 = first_of(p), e1 = second_of(p);
         if (e0 < d) dst[e0] = from_f32<T>(a[c]);
         if (e1 < d) dst[e1] = from_f32<T>(b[c]);
@@ -246,12 +247,22 @@ extern "C" int cib_window_attention_prep(void* qkv, int dtype, int stride, const
     const int blocks = (int)((warps + kPrepWarps - 1) / kPrepWarps);
     AnyVec lam{lambda, lambda_dtype == kBF16};
     PrepOptions opt{bias, q_gain, k_gain, norm, norm_first, rot_half, has_temp, temp_coef, temp_every};
-    if (dtype == kF32)
-        window_attention_prep_kernel<float><<<blocks, kPrepWarps * 32, 0, stream>>>((float*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const float*)v_first, v_first_stride, lam, lambda != nullptr, (float*)cache, num_slots, page_size, num_tokens, opt);
-    else if (dtype == kBF16)
-        window_attention_prep_kernel<__nv_bfloat16><<<blocks, kPrepWarps * 32, 0, stream>>>((__nv_bfloat16*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const __nv_bfloat16*)v_first, v_first_stride, lam, lambda != nullptr, (__nv_bfloat16*)cache, num_slots, page_size, num_tokens, opt);
-    else
-        CIB_REQUIRE(false, "window_attention_prep: bad dtype %d", dtype);
+#define CIB_PREP(T, C)                                                                                                        \
+    window_attention_prep_kernel<T, C><<<blocks, kPrepWarps * 32, 0, stream>>>(                                               \
+        (T*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const T*)v_first, v_first_stride, lam,    \
+        lambda != nullptr, (T*)cache, num_slots, page_size, num_tokens, opt)
+#define CIB_PREP_BY_SIZE(T)                                                                                                   \
+    {                                                                                                                         \
+        if (d <= 64) CIB_PREP(T, 1);                                                                                          \
+        else if (d <= 128) CIB_PREP(T, 2);                                                                                    \
+        else if (d <= 256) CIB_PREP(T, 4);                                                                                    \
+        else CIB_PREP(T, 8);                                                                                                  \
+    }
+    if (dtype == kF32) CIB_PREP_BY_SIZE(float)
+    else if (dtype == kBF16) CIB_PREP_BY_SIZE(__nv_bfloat16)
+    else CIB_REQUIRE(false, "window_attention_prep: bad dtype %d", dtype);
+#undef CIB_PREP_BY_SIZE
+#undef CIB_PREP
     CIB_LAUNCH_CHECK("window_attention_prep");
     return 0;
 }
