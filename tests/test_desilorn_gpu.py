@@ -521,7 +521,8 @@ def test_attention_of_many_shapes(dtype, H, G, d, dv, size, chunked, bias, sinks
     _close(got, want, dtype, "attention output")
 
 
-@pytest.mark.parametrize("d,dv,H,G", [(64, 32, 4, 2), (64, 64, 8, 2), (128, 128, 2, 2), (128, 64, 6, 1), (64, 128, 4, 4), (128, 32, 3, 1)])
+@pytest.mark.parametrize("d,dv,H,G", [(64, 32, 4, 2), (64, 64, 8, 2), (128, 128, 2, 2), (128, 64, 6, 1), (64, 128, 4, 4), (128, 32, 3, 1),
+                                      (64, 64, 5, 1), (128, 128, 14, 2), (64, 32, 10, 2), (128, 64, 16, 1)])
 def test_attention_on_the_tensor_cores(d, dv, H, G):
     """The tensor-core kernel against plain attention over the same cached rows: windows and chunks that start inside and
     between key tiles, requests of one token beside long portions, and a key made to stand out at every edge."""
