@@ -36,6 +36,10 @@ SIZES = {
                   expert_ff=768, shared_ff=768, vocab=32768, layers=4, kv_heads=8, head_dim=128,
                   window=512, keep_first=4, side_dim=64, delta_heads=16, delta_kv_heads=8, delta_dim=64, delta_vdim=64,
                   memory_heads=4, memory_dim=128, memory_vdim=256),
+    "medium": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, q_rank=1024, kv_rank=384, ff=6144, experts=16, top=2,
+                   expert_ff=1024, shared_ff=1536, vocab=32768, layers=4, kv_heads=8, head_dim=128,
+                   window=1024, keep_first=4, side_dim=128, delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128,
+                   memory_heads=4, memory_dim=256, memory_vdim=512),
     "large": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, ff=12288, experts=32, top=2,
                   expert_ff=1536, shared_ff=3072, vocab=32768, layers=4, kv_heads=8, head_dim=128,
                   window=1024, keep_first=4, side_dim=256, delta_heads=32, delta_kv_heads=16, delta_dim=128, delta_vdim=128,

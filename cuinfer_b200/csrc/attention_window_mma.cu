@@ -57,7 +57,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                             int num_splits, float* __restrict__ partial, int chunked, const float* __restrict__ slopes,
                             const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ int s_req, s_tile;
+    __shared__ int s_req, s_tile, s_q0, s_n, s_seq;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = lane & 3, qrow = lane >> 2;
     const int kvh = blockIdx.y;
@@ -65,24 +65,59 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     constexpr int kCK = DK / 8, kCV = DV / 8;
     constexpr float kLog2e = 1.4426950408889634f;
 
-    if (tid == 0) {
-        int t = blockIdx.x, r = 0;
-        for (; r < num_requests; ++r) {
-            const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kWmM - 1) / kWmM;
-            if (t < tiles) break;
-            t -= tiles;
+    // Which request and which of its row tiles this CTA has: the first warp reads 32 requests' bounds at once and finds
+    // the tile by a prefix sum over its lanes (one trip to memory instead of one per request before this one); the
+    // request's start, token count and length come back from the same trip.
+    if (warp == 0) {
+        int t = blockIdx.x, found = num_requests, tile = 0, q0_f = 0, n_f = 0, seq_f = 0;
+        for (int base = 0; base < num_requests; base += 32) {
+            const int rr = base + lane;
+            int q0_l = 0, n_l = 0, seq_l = 0;
+            if (rr < num_requests) {
+                q0_l = query_start_loc[rr];
+                n_l = query_start_loc[rr + 1] - q0_l;
+                seq_l = seq_lens[rr];
+            }
+            const int tiles = n_l > 0 ? (n_l * g + kWmM - 1) / kWmM : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += v;
+            }
+            const int excl = incl - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, t >= excl && t < incl);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                found = base + src;
+                tile = t - __shfl_sync(0xffffffffu, excl, src);
+                q0_f = __shfl_sync(0xffffffffu, q0_l, src);
+                n_f = __shfl_sync(0xffffffffu, n_l, src);
+                seq_f = __shfl_sync(0xffffffffu, seq_l, src);
+                break;
+            }
+            t -= __shfl_sync(0xffffffffu, incl, 31);
         }
-        s_req = r;
-        s_tile = t;
+        if (lane == 0) {
+            s_req = found;
+            s_tile = tile;
+            s_q0 = q0_f;
+            s_n = n_f;
+            s_seq = seq_f;
+        }
     }
     __syncthreads();
     const int r = s_req;
     if (r >= num_requests) return;
-    const int q0 = query_start_loc[r];
-    const int n = query_start_loc[r + 1] - q0;
-    const int seq_len = seq_lens[r];
+    const int q0 = s_q0;
+    const int n = s_n;
+    const int seq_len = s_seq;
     const int rows_total = n * g;
     const int row0 = s_tile * kWmM;
+    // A tile with rows in its first sixteen only (a decode step; a short portion; a request's last rows): the four warps
+    // share out the KEYS of every key tile instead, sixteen each against the same rows, and merge at the end.
+    const bool split_keys = rows_total - row0 <= 16;
+    const int wrow = split_keys ? 0 : warp * 16;      // this warp's first row of the tile
     const int* table = block_table + (size_t)r * table_stride;
 
     constexpr int kStageElems = kWmN * (DK + DV);
@@ -141,7 +176,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     uint32_t qf[DK / 16][4];
     {
         const int mat = lane >> 3, rr = lane & 7;
-        const int row = warp * 16 + (mat & 1) * 8 + rr;
+        const int row = wrow + (mat & 1) * 8 + rr;
 #pragma unroll
         for (int kt = 0; kt < DK / 16; ++kt) {
             const int chunk = 2 * kt + (mat >> 1);
@@ -154,7 +189,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     float slope_row[2];          // the distance bias of the row's head, in base-2 units
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int grow = row0 + warp * 16 + qrow + 8 * h;
+        const int grow = row0 + wrow + qrow + 8 * h;
         row_ok[h] = grow < rows_total;
         pos_row[h] = row_ok[h] ? seq_len - n + grow / g : -1;
         lo_row[h] = row_ok[h] ? window_start(pos_row[h]) : 0;
@@ -162,7 +197,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     }
 
     // first and last position among this warp's rows: a key tile that every one of them sees whole needs no mask
-    const int warp_row_first = row0 + warp * 16, warp_row_last = min(row0 + warp * 16 + 15, rows_total - 1);
+    const int warp_row_first = row0 + wrow, warp_row_last = min(row0 + wrow + 15, rows_total - 1);
     const bool warp_has_rows = warp_row_first < rows_total;
     const int warp_pos_min = seq_len - n + (warp_has_rows ? warp_row_first : 0) / g;
     const int warp_pos_max = seq_len - n + (warp_has_rows ? warp_row_last : 0) / g;
@@ -186,6 +221,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         const __nv_bfloat16* sK = stage_k((t - t_begin) % kWmStages);      // the first tile of a CTA goes to stage 0: the queries borrow stage 1
         const __nv_bfloat16* sV = stage_v((t - t_begin) % kWmStages);
 
+        if (warp_has_rows) {      // a decode step's tile has rows in its first warp only: the others just copy and wait
         float s[kWmN / 8][4];
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
@@ -195,6 +231,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
             for (int kt = 0; kt < DK / 16; ++kt) {
 #pragma unroll
                 for (int np = 0; np < kWmN / 16; ++np) {
+                    if (split_keys && np != warp) continue;
                     const int krow = np * 16 + (mat >> 1) * 8 + rr;
                     const int chunk = 2 * kt + (mat & 1);
                     uint32_t b[4];
@@ -209,6 +246,10 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) {
+            if (split_keys && (nt >> 1) != warp) {
+                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = -INFINITY;
+                continue;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int h = e >> 1;
@@ -243,6 +284,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         }
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) {
+            if (split_keys && (nt >> 1) != warp) continue;      // their weights are not read: the second product skips them
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float mref = m_run[e >> 1];
@@ -257,6 +299,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
             const int mat = lane >> 3, rr = lane & 7;
 #pragma unroll
             for (int kp = 0; kp < kWmN / 16; ++kp) {
+                if (split_keys && kp != warp) continue;
                 uint32_t pf[4];
                 pf[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
                 pf[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
@@ -273,9 +316,50 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                 }
             }
         }
+        }
         __syncthreads();      // every warp is done with this stage before it is filled again
     }
     cp_async_wait<0>();
+
+    if (split_keys) {
+        // Warps 1 to 3 leave their running maxima, sums and outputs in shared memory, lane by lane (the fragments of all
+        // four warps cover the same rows and columns); the first warp folds them into its own and goes on alone.
+        constexpr int kVals = DV / 2 + 4;
+        float* scratch = reinterpret_cast<float*>(smem_raw);      // 3 x kVals x 32 floats: the stages are free by now
+        if (warp > 0) {
+            float* mine = scratch + (size_t)(warp - 1) * kVals * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < DV / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine[(i * 4 + e) * 32] = o[i][e];
+            }
+            mine[(DV / 2) * 32] = m_run[0];
+            mine[(DV / 2 + 1) * 32] = m_run[1];
+            mine[(DV / 2 + 2) * 32] = l_run[0];
+            mine[(DV / 2 + 3) * 32] = l_run[1];
+        }
+        __syncthreads();
+        if (warp > 0) return;
+#pragma unroll 1
+        for (int w = 0; w < kWmWarps - 1; ++w) {
+            const float* theirs = scratch + (size_t)w * kVals * 32 + lane;
+            float mine_f[2], theirs_f[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float m_w = theirs[(DV / 2 + h) * 32];
+                const float m_new = fmaxf(m_run[h], m_w);
+                mine_f[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+                theirs_f[h] = m_w == -INFINITY ? 0.f : exp2f(m_w - m_new);
+                m_run[h] = m_new;
+                l_run[h] = l_run[h] * mine_f[h] + theirs[(DV / 2 + 2 + h) * 32] * theirs_f[h];
+            }
+#pragma unroll
+            for (int i = 0; i < DV / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[i][e] = o[i][e] * mine_f[e >> 1] + theirs[(i * 4 + e) * 32] * theirs_f[e >> 1];
+            }
+        }
+    }
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -283,7 +367,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         if (!row_ok[h]) continue;
-        const int grow = row0 + warp * 16 + qrow + 8 * h;
+        const int grow = row0 + wrow + qrow + 8 * h;
         const int tl = grow / g, hi = grow % g;
         float rescale = 1.f;
         if (sinks && num_splits == 1) {                // the sink joins the denominator (the merge kernel adds it otherwise)
