@@ -47,7 +47,7 @@ __device__ __forceinline__ void wm_load_kv_row(__nv_bfloat16* sK, __nv_bfloat16*
     }
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool kFewRows>
 __global__ void __launch_bounds__(kWmWarps * 32, 3)
 window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                             int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
@@ -116,7 +116,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     const int row0 = s_tile * kWmM;
     // A tile with rows in its first sixteen only (a decode step; a short portion; a request's last rows): the four warps
     // share out the KEYS of every key tile instead, sixteen each against the same rows, and merge at the end.
-    const bool split_keys = rows_total - row0 <= 16;
+    // (Compiled in only for launches whose requests all have so few rows: the row-parallel form pays nothing for it.)
+    const bool split_keys = kFewRows && rows_total - row0 <= 16;
     const int wrow = split_keys ? 0 : warp * 16;      // this warp's first row of the tile
     const int* table = block_table + (size_t)r * table_stride;
 
@@ -221,7 +222,6 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         const __nv_bfloat16* sK = stage_k((t - t_begin) % kWmStages);      // the first tile of a CTA goes to stage 0: the queries borrow stage 1
         const __nv_bfloat16* sV = stage_v((t - t_begin) % kWmStages);
 
-        if (warp_has_rows) {      // a decode step's tile has rows in its first warp only: the others just copy and wait
         float s[kWmN / 8][4];
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
@@ -316,7 +316,6 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                 }
             }
         }
-        }
         __syncthreads();      // every warp is done with this stage before it is filled again
     }
     cp_async_wait<0>();
@@ -399,6 +398,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
 }
 
 // out[row] = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M) over the splits' partial results; a warp per (token, head).
+// Lane i holds split i's (and split i + 32's) maximum and sum, so the weights come from one trip to memory and a
+// reduction over the lanes; the columns then read all splits' outputs with the weights handed round by shuffles.
 __global__ void window_attention_merge_kernel(const float* __restrict__ partial, int num_splits, int dv,
                                               __nv_bfloat16* __restrict__ out, int out_stride, int nq, int rows,
                                               const float* __restrict__ sinks) {
@@ -406,24 +407,44 @@ __global__ void window_attention_merge_kernel(const float* __restrict__ partial,
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const float* base = partial + (size_t)row * num_splits * (dv + 2);
-    float M = -INFINITY;
-    for (int i = 0; i < num_splits; ++i) M = fmaxf(M, base[(size_t)i * (dv + 2) + dv]);
-    const float sink = sinks ? sinks[row % nq] * 1.4426950408889634f : -INFINITY;     // maxima are in base-2 units
-    M = fmaxf(M, sink);
-    float L = sinks ? exp2f(sink - M) : 0.f;
-    for (int i = 0; i < num_splits; ++i) {
-        const float mi = base[(size_t)i * (dv + 2) + dv];
-        if (mi != -INFINITY) L += base[(size_t)i * (dv + 2) + dv + 1] * exp2f(mi - M);
+    float m_l[2], l_l[2], w_l[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = lane + 32 * k;
+        m_l[k] = i < num_splits ? base[(size_t)i * (dv + 2) + dv] : -INFINITY;
+        l_l[k] = i < num_splits ? base[(size_t)i * (dv + 2) + dv + 1] : 0.f;
     }
+    const float sink = sinks ? sinks[row % nq] * 1.4426950408889634f : -INFINITY;     // maxima are in base-2 units
+    float M = fmaxf(fmaxf(m_l[0], m_l[1]), sink);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+    float L = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        w_l[k] = m_l[k] == -INFINITY ? 0.f : exp2f(m_l[k] - M);
+        L += l_l[k] * w_l[k];
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
+    if (sinks) L += exp2f(sink - M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     __nv_bfloat16* dst = out + (size_t)(row / nq) * out_stride + (size_t)(row % nq) * dv;
-    for (int c = lane; c < dv; c += 32) {
-        float acc = 0.f;
-        for (int i = 0; i < num_splits; ++i) {
-            const float mi = base[(size_t)i * (dv + 2) + dv];
-            if (mi != -INFINITY) acc = fmaf(base[(size_t)i * (dv + 2) + c], exp2f(mi - M), acc);
-        }
-        dst[c] = __float2bfloat16_rn(acc * inv);
+    // every lane walks every split, so that the shuffles meet; a split's four loads of a lane are issued together
+    // (value sizes up to 128, which is all the tensor-core kernel takes), whatever the weight, and count only if it is not zero
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int i = 0; i < num_splits; ++i) {
+        const float w = __shfl_sync(0xffffffffu, i < 32 ? w_l[0] : w_l[1], i & 31);
+        const float* src = base + (size_t)i * (dv + 2);
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = lane + 32 * k < dv ? src[lane + 32 * k] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = w != 0.f ? fmaf(v[k], w, acc[k]) : acc[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (lane + 32 * k < dv) dst[lane + 32 * k] = __float2bfloat16_rn(acc[k] * inv);
     }
 }
 
@@ -432,12 +453,13 @@ static int launch_window_mma(const void* q, int q_stride, void* out, int out_str
                              int page_size, const int* block_table, int table_stride, const int* query_start_loc,
                              const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, float cap,
                              int window, int keep_first, int num_splits, float* partial, int num_tokens, int chunked,
-                             const float* slopes, const float* sinks, cudaStream_t stream) {
+                             bool few_rows, const float* slopes, const float* sinks, cudaStream_t stream) {
     const size_t smem = (size_t)(kWmStages * kWmN * (DK + DV)) * sizeof(__nv_bfloat16);
-    static SmemLimit limit;
-    if (int rc = raise_smem_limit(limit, window_attention_mma_kernel<DK, DV>, smem, "window_attention_mma")) return rc;
+    static SmemLimit limit, limit_few;
+    auto kernel = few_rows ? window_attention_mma_kernel<DK, DV, true> : window_attention_mma_kernel<DK, DV, false>;
+    if (int rc = raise_smem_limit(few_rows ? limit_few : limit, kernel, smem, "window_attention_mma")) return rc;
     dim3 grid(num_tiles, nkv, num_splits);
-    window_attention_mma_kernel<DK, DV><<<grid, kWmWarps * 32, smem, stream>>>(
+    kernel<<<grid, kWmWarps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
         page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv, scale, cap, window, keep_first,
         num_splits, partial, chunked, slopes, sinks);
@@ -462,12 +484,14 @@ extern "C" int cib_window_attention_mma_supports(int dim, int vdim, int nq, int 
 // tile leave).  num_splits > 1: every row tile's key tiles are shared out to so many CTAs, which leave float32 partial
 // results in `partial` ([tokens * nq][num_splits][vdim + 2]: output, running maximum, sum) for a second kernel to merge.
 // chunked: the window is a chunk (keys from floor(i / window) * window on); slopes, sinks: float32 [nq] or null.
+// few_rows: no request has more than 16 rows (tokens * nq / nkv) in this launch, e.g. a decode step: the form whose
+// warps share out a tile's keys instead of its rows runs (any tile with more rows still takes the row-parallel path).
 extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                         int num_pages, int page_size, const int* block_table, int table_stride,
                                         const int* query_start_loc, const int* seq_lens, int num_requests, int num_tiles,
                                         int nq, int nkv, int dim, int vdim, float scale, float cap, int window,
                                         int keep_first, int num_splits, float* partial, int num_tokens, int chunked,
-                                        const float* slopes, const float* sinks, cudaStream_t stream) {
+                                        int few_rows, const float* slopes, const float* sinks, cudaStream_t stream) {
     CIB_REQUIRE(cib_window_attention_mma_supports(dim, vdim, nq, nkv), "window_attention_mma: sizes %d / %d are not taken by this kernel", dim, vdim);
     CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535, "window_attention_mma: bad sizes");
     CIB_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || partial), "window_attention_mma: %d splits need room for their partial results", num_splits);
@@ -479,7 +503,7 @@ extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, 
     if (dim == DKv && vdim == DVv)                                                                                           \
         return launch_window_mma<DKv, DVv>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, \
                                            query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, cap, window,     \
-                                           keep_first, num_splits, partial, num_tokens, chunked, slopes, sinks, stream)
+                                           keep_first, num_splits, partial, num_tokens, chunked, few_rows != 0, slopes, sinks, stream)
     CIB_WM(64, 32);
     CIB_WM(64, 64);
     CIB_WM(64, 128);

@@ -84,7 +84,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I,
                                       _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _P, _P],
-        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _I, _P, _P, _P],
+        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P],
         "cib_hyper_stream": [_P, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _P],
         "cib_hyper_gather": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
@@ -1100,6 +1100,7 @@ def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
         raise KernelError("window_attention_mma: bfloat16 rows, out [T, H * vdim]")
     g = num_heads // num_kv_heads
     tiles = sum((n * g + 63) // 64 for n in query_lens)
+    few_rows = all(n * g <= 16 for n in query_lens)      # a decode step: the warps of a tile share out its keys, not its rows
     splits = max(1, min(int(splits), 64))
     partial = torch.empty((T * num_heads, splits, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     rc = library().cib_window_attention_mma(
@@ -1107,7 +1108,7 @@ def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
         cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
         _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32), seq_lens.numel(), tiles,
         num_heads, num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), splits,
-        _cuda(partial, "partial") if partial is not None else None, T, 1 if chunked and window else 0,
+        _cuda(partial, "partial") if partial is not None else None, T, 1 if chunked and window else 0, 1 if few_rows else 0,
         _f32_vec(slopes, num_heads, "slopes"), _f32_vec(sinks, num_heads, "sinks"), _stream())
     _check(rc, "window_attention_mma")
     _count()

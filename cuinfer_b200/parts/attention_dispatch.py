@@ -78,7 +78,7 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, kv
 def window_decode_splits(ctx: StepContext, num_kv_heads: int, window: int, keep_first: int) -> int:
     """Over how many CTAs a decode step shares the key tiles of a (request, key head): one CTA walks them one after the
     other otherwise, and a step of few requests leaves most SMs idle.  At least two tiles a CTA, at most eight splits,
-    and no more CTAs than two a SM."""
+    and no more CTAs than the three a SM that are resident at once (a second round of CTAs costs more than it saves)."""
     if not ctx.decode_only:
         return 1
     keys = max(1, ctx.max_seq_len)
@@ -86,7 +86,7 @@ def window_decode_splits(ctx: StepContext, num_kv_heads: int, window: int, keep_
         keys = min(keys, window + 63) + (64 if keep_first else 0)
     tiles = -(-keys // 64)
     ctas = max(1, ctx.num_requests * num_kv_heads)
-    return max(1, min(8, tiles // 2, 296 // ctas))
+    return max(1, min(8, tiles // 2, 444 // ctas))
 
 
 _FORCE_GENERIC_WINDOW = os.environ.get("CUINFER_B200_WINDOW_ATTENTION", "") == "generic"
