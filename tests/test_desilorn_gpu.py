@@ -558,6 +558,27 @@ def test_decode_steps_share_a_mask_over_several_ctas(splits):
             _close(got, want, dtype, f"query {n - 1} with key {j} standing out over {splits} splits (chunks: {chunked})")
 
 
+@pytest.mark.parametrize("H,G,d,dv,new", [(3, 3, 64, 32, 1), (10, 2, 128, 128, 3), (16, 1, 64, 64, 1), (16, 2, 128, 64, 2), (12, 4, 64, 128, 5)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_steps_of_few_rows_share_the_keys_of_a_tile(H, G, d, dv, new, splits):
+    """A step whose requests all bring at most sixteen rows (tokens x query heads of a key head) runs the form of the
+    tensor-core kernel whose four warps take a quarter of every key tile each: one to sixteen rows, a key made to stand
+    out in every quarter of a tile and at the window's and the chunk's edges, requests of a few keys and of many."""
+    dtype = torch.bfloat16
+    assert new * (H // G) <= 16
+    sink_list = [0.5 * (h % 5) - 1.0 for h in range(H)]
+    n, size = 700, 200
+    lengths, news = [n, new, 97 + new, 333], [new, new, new, new]
+    for chunked in (False, True):
+        edges = [j for j, _ in _edge_cases(n - 1, size, chunked)]
+        first = (n - 1) // size * size if chunked else n - size
+        quarters = [first // 64 * 64 + 64 + 16 * w + 3 * w for w in range(4)]      # one key in each warp's share of a whole tile
+        for j in edges + quarters:
+            got, want = _attention_case(dtype, H, G, d, dv, lengths, news, 16, 11 + j, size, chunked, not chunked,
+                                        "zero" if chunked else sink_list, sharpen={new - 1: j}, tensor_cores=True, splits=splits)
+            _close(got, want, dtype, f"{new} tokens x {H // G} heads with key {j} standing out (chunks: {chunked}, {splits} splits)")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,dims", [(4, 2, 10, 6, 6), (3, 1, 16, 16, 16), (2, 2, 64, 32, 2), (5, 5, 7, 9, 0)])
 def test_bias_head_norm_rotation_in_halves_and_cache_write(dtype, H, G, d, dv, dims):
