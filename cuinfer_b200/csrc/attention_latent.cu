@@ -12,7 +12,8 @@
 //  * latent_prep: per token, RMS norm of the query latent (written out for the query up-projection), RMS norm of the
 //    key/value latent and rotary encoding of the shared key part, both written to the token's cache slot.  Pairs are
 //    interleaved, (2i, 2i+1), over the first `rot_dims` of the dr values; the angle is position * freq[i] in 32 bits
-//    with the full-range sine and cosine.
+//    with the full-range sine and cosine, both multiplied by `rot_gain` (1: a pure rotation).  Without a query latent
+//    (no output for it) only the cache row is written.
 //  * latent_attention_generic: a warp per (query token, head), any sizes up to rk = 1024, 32-bit throughout with
 //    the exact exponential; the query's rotary part is encoded as it is loaded.  This is the 32-bit path and the
 //    fallback of the tensor-core kernels.
@@ -25,8 +26,9 @@ namespace cib {
 template <typename T>
 __global__ void latent_prep_kernel(const T* __restrict__ proj, int stride, int q_off, int rq, int kv_off, int rk, int dr,
                                    AnyVec q_gain, AnyVec kv_gain, float eps, const int* __restrict__ positions,
-                                   const float* __restrict__ freq, int rot_dims, const int* __restrict__ slot_mapping,
-                                   T* __restrict__ cache, long long num_slots, T* __restrict__ cq_out, int cq_stride) {
+                                   const float* __restrict__ freq, int rot_dims, float rot_gain,
+                                   const int* __restrict__ slot_mapping, T* __restrict__ cache, long long num_slots,
+                                   T* __restrict__ cq_out, int cq_stride) {
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const T* row = proj + (size_t)t * stride;
@@ -59,6 +61,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int stride, int q
         if (2 * i + 1 < rot_dims) {
             float s, c;
             sincosf(pos * freq[i], &s, &c);
+            s *= rot_gain;
+            c *= rot_gain;
             dst[rk + 2 * i] = from_f32<T>(u * c - v * s);
             dst[rk + 2 * i + 1] = from_f32<T>(v * c + u * s);
         } else {
@@ -79,7 +83,7 @@ __global__ void latent_attention_generic_kernel(
     int out_stride, const T* __restrict__ cache, int num_pages, int page_size, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ query_start_loc, const int* __restrict__ seq_lens,
     const int* __restrict__ token_request, const int* __restrict__ positions, const float* __restrict__ freq, int rot_dims,
-    AnyVec sinks, int has_sink, int H, int rk, int dr, float scale, int window) {
+    float rot_gain, AnyVec sinks, int has_sink, int H, int rk, int dr, float scale, int window) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -104,6 +108,8 @@ __global__ void latent_attention_generic_kernel(
         if (2 * i + 1 < rot_dims) {
             float s, c;
             sincosf(fpos * freq[i], &s, &c);
+            s *= rot_gain;
+            c *= rot_gain;
             qs[rk + 2 * i] = (u * c - v * s) * scale;
             qs[rk + 2 * i + 1] = (v * c + u * s) * scale;
         } else {
@@ -174,7 +180,7 @@ using namespace cib;
 
 extern "C" int cib_latent_prep(const void* proj, int dtype, int stride, int q_off, int rq, int kv_off, int rk, int dr,
                                const void* q_gain, const void* kv_gain, int gain_dtype, float eps, const int* positions,
-                               const float* freq, int rot_dims, const int* slot_mapping, void* cache,
+                               const float* freq, int rot_dims, float rot_gain, const int* slot_mapping, void* cache,
                                long long num_slots, void* cq_out, int cq_stride, int num_tokens, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && rq >= 0 && rk > 0 && dr >= 0, "latent_prep: bad sizes T=%d rq=%d rk=%d dr=%d", num_tokens, rq, rk, dr);
     CIB_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0, "latent_prep: %d rotary dimensions in a part of %d", rot_dims, dr);
@@ -183,9 +189,9 @@ extern "C" int cib_latent_prep(const void* proj, int dtype, int stride, int q_of
     if (num_tokens == 0) return 0;
     AnyVec qg{q_gain, gain_dtype == kBF16}, kg{kv_gain, gain_dtype == kBF16};
     if (dtype == kF32)
-        latent_prep_kernel<float><<<num_tokens, 128, 0, stream>>>((const float*)proj, stride, q_off, rq, kv_off, rk, dr, qg, kg, eps, positions, freq, rot_dims, slot_mapping, (float*)cache, num_slots, (float*)cq_out, cq_stride);
+        latent_prep_kernel<float><<<num_tokens, 128, 0, stream>>>((const float*)proj, stride, q_off, rq, kv_off, rk, dr, qg, kg, eps, positions, freq, rot_dims, rot_gain, slot_mapping, (float*)cache, num_slots, (float*)cq_out, cq_stride);
     else if (dtype == kBF16)
-        latent_prep_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>((const __nv_bfloat16*)proj, stride, q_off, rq, kv_off, rk, dr, qg, kg, eps, positions, freq, rot_dims, slot_mapping, (__nv_bfloat16*)cache, num_slots, (__nv_bfloat16*)cq_out, cq_stride);
+        latent_prep_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>((const __nv_bfloat16*)proj, stride, q_off, rq, kv_off, rk, dr, qg, kg, eps, positions, freq, rot_dims, rot_gain, slot_mapping, (__nv_bfloat16*)cache, num_slots, (__nv_bfloat16*)cq_out, cq_stride);
     else
         CIB_REQUIRE(false, "latent_prep: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("latent_prep");
@@ -196,12 +202,12 @@ template <typename T, typename TQ>
 static void launch_latent_generic(int acc, dim3 grid, size_t smem, cudaStream_t stream, const void* q_abs, int qa_stride,
                                   const void* q, int q_stride, int dn, void* out, int out_stride, const void* cache,
                                   int num_pages, int page_size, const int* bt, int ts, const int* qsl, const int* sl,
-                                  const int* tr, const int* positions, const float* freq, int rot_dims, AnyVec sinks,
-                                  int has_sink, int H, int rk, int dr, float scale, int window) {
+                                  const int* tr, const int* positions, const float* freq, int rot_dims, float rot_gain,
+                                  AnyVec sinks, int has_sink, int H, int rk, int dr, float scale, int window) {
 #define CIB_LATENT_GO(A)                                                                                                  \
     latent_attention_generic_kernel<T, TQ, A><<<grid, kLatentWarps * 32, smem, stream>>>(                                  \
         (const TQ*)q_abs, qa_stride, (const T*)q, q_stride, dn, (T*)out, out_stride, (const T*)cache, num_pages, page_size, \
-        bt, ts, qsl, sl, tr, positions, freq, rot_dims, sinks, has_sink, H, rk, dr, scale, window)
+        bt, ts, qsl, sl, tr, positions, freq, rot_dims, rot_gain, sinks, has_sink, H, rk, dr, scale, window)
     if (acc <= 4) CIB_LATENT_GO(4);
     else if (acc <= 8) CIB_LATENT_GO(8);
     else if (acc <= 16) CIB_LATENT_GO(16);
@@ -213,9 +219,9 @@ extern "C" int cib_latent_attention_generic(const void* q_abs, int qa_dtype, int
                                             int q_stride, int dn, void* out, int out_stride, const void* cache,
                                             int num_pages, int page_size, const int* block_table, int table_stride,
                                             const int* query_start_loc, const int* seq_lens, const int* token_request,
-                                            const int* positions, const float* freq, int rot_dims, const void* sinks,
-                                            int sink_dtype, int num_tokens, int H, int rk, int dr, float scale, int window,
-                                            cudaStream_t stream) {
+                                            const int* positions, const float* freq, int rot_dims, float rot_gain,
+                                            const void* sinks, int sink_dtype, int num_tokens, int H, int rk, int dr,
+                                            float scale, int window, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && H > 0 && rk > 0 && dr >= 0 && dn >= 0, "latent_attention: bad sizes T=%d H=%d rk=%d dr=%d", num_tokens, H, rk, dr);
     CIB_REQUIRE(rk <= 1024, "latent_attention: latent size %d exceeds 1024", rk);
     CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "latent_attention: bad cache geometry");
@@ -229,11 +235,11 @@ extern "C" int cib_latent_attention_generic(const void* q_abs, int qa_dtype, int
     AnyVec sk{sinks, sink_dtype == kBF16};
     const int has_sink = sinks != nullptr;
     if (dtype == kF32)
-        launch_latent_generic<float, float>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, sk, has_sink, H, rk, dr, scale, window);
+        launch_latent_generic<float, float>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, rot_gain, sk, has_sink, H, rk, dr, scale, window);
     else if (dtype == kBF16 && qa_dtype == kF32)
-        launch_latent_generic<__nv_bfloat16, float>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, sk, has_sink, H, rk, dr, scale, window);
+        launch_latent_generic<__nv_bfloat16, float>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, rot_gain, sk, has_sink, H, rk, dr, scale, window);
     else if (dtype == kBF16)
-        launch_latent_generic<__nv_bfloat16, __nv_bfloat16>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, sk, has_sink, H, rk, dr, scale, window);
+        launch_latent_generic<__nv_bfloat16, __nv_bfloat16>(acc, grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, cache, num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, token_request, positions, freq, rot_dims, rot_gain, sk, has_sink, H, rk, dr, scale, window);
     else
         CIB_REQUIRE(false, "latent_attention: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("latent_attention_generic");

@@ -9,7 +9,9 @@
 // columns, O += P V over the first rk columns of the same shared-memory tile (the values ARE the latents).  A warp owns
 // 16 rows; for rk > 256 eight warps share them in pairs, each computing S again and keeping half of the value columns
 // (128 accumulator registers a thread).  The query's rotary part is encoded as the tile is loaded; softmax statistics
-// are 32-bit in the log2 domain; the sink starts a row's running maximum and counts once in its sum.
+// are 32-bit in the log2 domain; the sink starts a row's running maximum and counts once in its sum.  With a window
+// (query i sees key j when 0 <= i - j < window) a tile starts at the first key tile its first token sees and masks both
+// edges; cosine and sine of the rotation are multiplied by `rot_gain`.
 //
 // gridDim.z > 1 splits a tile's keys over CTAs (decode steps: few rows, long contexts).  Each split then writes its
 // running maximum, its sum and its unnormalised rows to a scratch buffer and a second kernel merges them with the sink.
@@ -28,7 +30,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
                             const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ query_start_loc,
                             const int* __restrict__ seq_lens, int num_requests, const float* __restrict__ freq, int rot_dims,
-                            const float* __restrict__ sinks, int H, int hb_log2, int rk, int dr, float scale_log2) {
+                            const float* __restrict__ sinks, int H, int hb_log2, int rk, int dr, float scale_log2,
+                            float rot_gain, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_req, s_tile;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -68,8 +71,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
 
     const int k_hi = seq_len - n + min(tok0 + TM, n);      // keys < k_hi are visible to the tile's last token
     const int tiles_all = (k_hi + kLmN - 1) / kLmN;
-    const int per = (tiles_all + splits - 1) / splits;
-    const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
+    // with a window the tile's first token sees nothing before its position - window + 1, and the later ones even less
+    const int tile_lo = window > 0 ? max(0, seq_len - n + tok0 - window + 1) / kLmN : 0;
+    const int per = (tiles_all - tile_lo + splits - 1) / splits;
+    const int t_begin = tile_lo + split * per, t_end = min(tiles_all, t_begin + per);
 
     // A key row of a tile is copied by blockDim.x / 32 threads, 16 bytes at a time.  Its page number is looked up one
     // tile ahead (`page_of`), so that no copy waits for a block-table entry: with the lookup inside the copy loop every
@@ -111,6 +116,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
                 if (2 * i + 1 < rot_dims) {
                     float sn, cs;
                     sincosf((float)(seq_len - n + tl) * freq[i], &sn, &cs);
+                    sn *= rot_gain;
+                    cs *= rot_gain;
                     const float a = u * cs - v * sn, b = v * cs + u * sn;
                     u = a;
                     v = b;
@@ -134,6 +141,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
         pos_row[h] = row_ok[h] ? seq_len - n + tl : -1;
     }
     const int warp_pos_min = seq_len - n + min(tok0 + ((rg * 16) >> hb_log2), n - 1);
+    const int warp_pos_max = seq_len - n + min(tok0 + ((rg * 16 + 15) >> hb_log2), n - 1);
 
     float o[RKH / 8][4];
 #pragma unroll
@@ -194,7 +202,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
             if (kt < ksteps) multiply(a0, b0);
         }
         // ---- scale, causal mask where the tile touches the diagonal, running maximum ----
-        const bool need_mask = key0 + kLmN - 1 > warp_pos_min;
+        const bool need_mask = key0 + kLmN - 1 > warp_pos_min || (window > 0 && key0 <= warp_pos_max - window);
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < kLmN / 8; ++nt) {
@@ -204,7 +212,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
                 float v = s[nt][e] * scale_log2;
                 if (need_mask) {
                     const int key = key0 + nt * 8 + quad * 2 + (e & 1);
-                    v = key <= pos_row[h] ? v : -INFINITY;
+                    v = (key <= pos_row[h] && (window <= 0 || key > pos_row[h] - window)) ? v : -INFINITY;
                 }
                 s[nt][e] = v;
                 mx[h] = fmaxf(mx[h], v);
@@ -323,14 +331,15 @@ template <int RKH, int CS, int RG>
 static int launch_latent_mma(dim3 grid, size_t smem, cudaStream_t stream, const void* q_abs, int qa_stride, const void* q,
                              int q_stride, int dn, void* out, int out_stride, float* part, const void* cache, int num_pages,
                              int page_size, const int* bt, int ts, const int* qsl, const int* sl, int R, const float* freq,
-                             int rot_dims, const float* sinks, int H, int hb_log2, int rk, int dr, float scale_log2) {
+                             int rot_dims, const float* sinks, int H, int hb_log2, int rk, int dr, float scale_log2,
+                             float rot_gain, int window) {
     static SmemLimit limit;
     auto kernel = latent_attention_mma_kernel<RKH, CS, RG>;
     if (smem > 48 * 1024 && raise_smem_limit(limit, kernel, 200 * 1024, "latent_attention_mma") != 0) return -2;
     kernel<<<grid, 32 * RG * CS, smem, stream>>>((const __nv_bfloat16*)q_abs, qa_stride, (const __nv_bfloat16*)q, q_stride, dn,
                                              (__nv_bfloat16*)out, out_stride, part, (const __nv_bfloat16*)cache, num_pages,
                                              page_size, bt, ts, qsl, sl, R, freq, rot_dims, sinks, H, hb_log2, rk, dr,
-                                             scale_log2);
+                                             scale_log2, rot_gain, window);
     return 0;
 }
 
@@ -363,7 +372,7 @@ extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const 
                                         const int* block_table, int table_stride, const int* query_start_loc,
                                         const int* seq_lens, int num_requests, int row_tiles, int tile_rows, const float* freq,
                                         int rot_dims, const float* sinks, int num_tokens, int H, int rk, int dr, float scale,
-                                        int splits, cudaStream_t stream) {
+                                        int splits, float rot_gain, int window, cudaStream_t stream) {
     CIB_REQUIRE(cib_latent_attention_mma_supports(rk, dr, dn), "latent_attention_mma: sizes rk=%d dr=%d are not taken", rk, dr);
     CIB_REQUIRE(num_tokens >= 0 && H > 0 && num_requests > 0 && row_tiles >= 0, "latent_attention_mma: bad sizes");
     CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "latent_attention_mma: bad cache geometry");
@@ -371,6 +380,7 @@ extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const 
     CIB_REQUIRE(qa_stride % 8 == 0 && out_stride % 2 == 0, "latent_attention_mma: rows must start on 16-byte boundaries");
     CIB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || scratch != nullptr), "latent_attention_mma: bad split");
     CIB_REQUIRE(tile_rows == 64 || tile_rows == 32, "latent_attention_mma: query tiles have 64 or 32 rows");
+    CIB_REQUIRE(window >= 0, "latent_attention_mma: window must be >= 0 (0 = all keys)");
     if (num_tokens == 0 || row_tiles == 0) return 0;
     const int hb_log2 = head_block_log2(H, tile_rows);
     dim3 grid(row_tiles, (H + (1 << hb_log2) - 1) >> hb_log2, splits);
@@ -380,7 +390,8 @@ extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const 
     int rc;
 #define CIB_LM_ARGS                                                                                                        \
     grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, scratch, cache, num_pages, page_size, block_table, \
-        table_stride, query_start_loc, seq_lens, num_requests, freq, rot_dims, sinks, H, hb_log2, rk, dr, scale_log2
+        table_stride, query_start_loc, seq_lens, num_requests, freq, rot_dims, sinks, H, hb_log2, rk, dr, scale_log2, \
+        rot_gain, window
 #define CIB_LM_GO(RKH, CS) \
     rc = tile_rows == 64 ? launch_latent_mma<RKH, CS, 4>(CIB_LM_ARGS) : launch_latent_mma<RKH, CS, 2>(CIB_LM_ARGS)
     if (rk <= 32) CIB_LM_GO(32, 1);

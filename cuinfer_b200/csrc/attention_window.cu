@@ -5,8 +5,9 @@
 //
 // Per token and head, with the query q and key k of d values and the value v of dv values:
 //   q, k, v += their biases (32-bit);
-//   rotation of the first `rot_dims` values by the angle pos * freq[i] (32-bit angle, full-range sine and cosine), in
-//   neighbouring pairs (2i, 2i+1) or in halves (i, i + rot_dims / 2);
+//   with `value_from_key` there is no v in the rows: v = k as it stands here, before norm and rotation;
+//   rotation of the first `rot_dims` values by the angle pos * freq[i] (32-bit angle, full-range sine and cosine, both
+//   multiplied by `rot_gain`), in neighbouring pairs (2i, 2i+1) or in halves (i, i + rot_dims / 2);
 //   q and k divided by their root mean square (eps inside the root) and multiplied by a gain of d values shared by all
 //   heads (null: no gain), after the rotation or, with `norm_first`, before it;
 //   q multiplied by the query temperature 1 + coef * ln(floor((pos + 1) / every) + 1);
@@ -37,10 +38,13 @@ struct PrepOptions {
     int has_temp;             // queries are multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
     float temp_coef;
     int temp_every;
+    int value_from_key;       // the packed rows are [q | k]: a token's value is its key as it stands before norm and rotation
+    float rot_gain;           // cosine and sine are both multiplied by this (1: a pure rotation)
 };
 
-// One warp per (token, vector): H query heads, G key heads, G value heads of the packed rows [q | k | v].  C: pairs of
-// values a lane holds (d <= 64 C).
+// One warp per (token, vector): H query heads, G key heads, G value heads of the packed rows [q | k | v] (with
+// `value_from_key` there are no value vectors: the key's warp stores the value too).  C: pairs of values a lane holds
+// (d <= 64 C).
 template <typename T, int C>
 __global__ void __launch_bounds__(kPrepWarps * 32)
 window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restrict__ positions,
@@ -49,7 +53,7 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
                              AnyVec lambda, int has_lambda, T* __restrict__ cache, long long num_slots, int page_size,
                              int num_tokens, PrepOptions opt) {
     const int lane = threadIdx.x & 31;
-    const int vectors = H + 2 * G;
+    const int vectors = opt.value_from_key ? H + G : H + 2 * G;
     const long long w = (long long)blockIdx.x * kPrepWarps + (threadIdx.x >> 5);
     if (w >= (long long)num_tokens * vectors) return;
     const int t = (int)(w / vectors), vec = (int)(w % vectors);
@@ -90,6 +94,15 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
         a[c] = e0 < d ? to_f32(x[e0]) + (bias ? bias[e0] : 0.f) : 0.f;
         b[c] = e1 < d ? to_f32(x[e1]) + (bias ? bias[e1] : 0.f) : 0.f;
     }
+    if (opt.value_from_key && is_key && store) {          // dv == d: the value is the key as projected
+        T* vdst = cache + (((size_t)(slot / page_size) * G + (vec - H)) * page_size + slot % page_size) * width + d;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int p = c * 32 + lane, e0 = first_of(p), e1 = second_of(p);
+            if (e0 < d) vdst[e0] = from_f32<T>(a[c]);
+            if (e1 < d) vdst[e1] = from_f32<T>(b[c]);
+        }
+    }
     auto normalise = [&]() {
         float ss = 0.f;
 #pragma unroll
@@ -110,6 +123,8 @@ window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restr
         if (p < half && second_of(p) < d) {
             float sn, cs;
             sincosf(pos * freq[p], &sn, &cs);
+            sn *= opt.rot_gain;
+            cs *= opt.rot_gain;
             const float u = a[c], v = b[c];
             a[c] = u * cs - v * sn;
             b[c] = v * cs + u * sn;
@@ -230,23 +245,26 @@ using namespace cib;
 
 // bias (float32 [H*d + G*d + G*dv]), q_gain / k_gain (float32 [d]) may be null.  norm: 0 none, 1 root mean square (with
 // the gains, if given); norm_first: before the rotation; rot_half: pairs (i, i + rot_dims / 2); has_temp: the query
-// temperature with temp_coef and temp_every.
+// temperature with temp_coef and temp_every; value_from_key: rows are [q | k] and a token's cached value is its key before
+// norm and rotation (dv == d); rot_gain: a factor on both cosine and sine.
 extern "C" int cib_window_attention_prep(void* qkv, int dtype, int stride, const int* positions, const int* slot_mapping,
                                          const float* freq, int rot_dims, float eps, int H, int G, int d, int dv,
                                          const void* v_first, int v_first_stride, const void* lambda, int lambda_dtype,
                                          void* cache, long long num_slots, int page_size, int num_tokens,
                                          const float* bias, const float* q_gain, const float* k_gain, int norm, int norm_first,
-                                         int rot_half, int has_temp, float temp_coef, int temp_every, cudaStream_t stream) {
+                                         int rot_half, int has_temp, float temp_coef, int temp_every, int value_from_key,
+                                         float rot_gain, cudaStream_t stream) {
     CIB_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "window_attention_prep: bad head counts or sizes");
     CIB_REQUIRE(d <= 64 * kPrepMaxPairsPerLane, "window_attention_prep: head size %d is beyond %d", d, 64 * kPrepMaxPairsPerLane);
     CIB_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq), "window_attention_prep: bad rotation");
     CIB_REQUIRE((v_first == nullptr) == (lambda == nullptr), "window_attention_prep: mixing needs both the values and the factor");
     CIB_REQUIRE(!has_temp || temp_every > 0, "window_attention_prep: the query temperature needs a positive period");
+    CIB_REQUIRE(!value_from_key || (d == dv && v_first == nullptr), "window_attention_prep: values taken from the keys have the keys' size and are not mixed");
     if (num_tokens == 0) return 0;
-    const long long warps = (long long)num_tokens * (H + 2 * G);
+    const long long warps = (long long)num_tokens * (value_from_key ? H + G : H + 2 * G);
     const int blocks = (int)((warps + kPrepWarps - 1) / kPrepWarps);
     AnyVec lam{lambda, lambda_dtype == kBF16};
-    PrepOptions opt{bias, q_gain, k_gain, norm, norm_first, rot_half, has_temp, temp_coef, temp_every};
+    PrepOptions opt{bias, q_gain, k_gain, norm, norm_first, rot_half, has_temp, temp_coef, temp_every, value_from_key, rot_gain};
 #define CIB_PREP(T, C)                                                                                                        \
     window_attention_prep_kernel<T, C><<<blocks, kPrepWarps * 32, 0, stream>>>(                                               \
         (T*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const T*)v_first, v_first_stride, lam,    \

@@ -12,7 +12,9 @@
 // The same kernels serve experts chosen by a router: `ids` null means that the table is indexed by the row itself
 // (table[t][k] = the k-th expert chosen for row t), `weights[t][k]` (32-bit, may be null) replaces the uniform weight,
 // and `act_kind` 1 selects the clamped gate  g = min(gate, limit), u = clamp(up, -limit, limit),
-// act = g * sigmoid(1.702 g) * (u + 1)  instead of silu(gate) * up.
+// act = g * sigmoid(1.702 g) * (u + 1)  instead of silu(gate) * up.  `act_kind` 2 is an expert WITHOUT a gate,
+// down_e( relu(up_e h)^2 ): its first matrix is [E][ff][W] (up rows only).  `base_gate` (32-bit, one number per row, `base_gate_stride` apart; may
+// be null): base is multiplied by sigmoid(base_gate[t]) as it is added (a shared expert with a gate of its own).
 #include "common.cuh"
 
 namespace cib {
@@ -21,8 +23,17 @@ constexpr int kMoeWarps = 8;
 constexpr int kMoeOutsPerBlock = 64;
 
 struct ExpertAct {
-    int kind;        // 0: silu(gate) * up;  1: the clamped gate described above
+    int kind;        // 0: silu(gate) * up;  1: the clamped gate described above;  2: no gate, relu(up)^2;  -1: nothing
     float limit;
+    __host__ __device__ __forceinline__ bool gated() const { return kind == 0 || kind == 1; }
+    // an expert without a gate: what becomes of its one product
+    __device__ __forceinline__ float single(float u) const {
+        if (kind == 2) {
+            u = fmaxf(u, 0.f);
+            return u * u;
+        }
+        return u;
+    }
     __device__ __forceinline__ float operator()(float g, float u) const {
         if (kind == 1) {
             g = fminf(g, limit);
@@ -93,15 +104,15 @@ moe_table_gate_up_kernel(const T* __restrict__ h, int h_stride, const int* __res
     const int id = ids ? ids[t] : t;
     const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + k] : -1;
     const bool ok = e >= 0 && e < experts;
-    const T* wg = gate_up + (size_t)(ok ? e : 0) * 2 * ff * width;
+    const bool gated = fn.gated();
+    const T* wg = gate_up + (size_t)(ok ? e : 0) * (gated ? 2 : 1) * ff * width;
     const T* wu = wg + (size_t)ff * width;
     const int j0 = blockIdx.y * kMoeOutsPerBlock;
     for (int j = j0 + warp; j < min(ff, j0 + kMoeOutsPerBlock); j += kMoeWarps) {
         float v = 0.f;
         if (ok) {
             const float g = dot_row(wg + (size_t)j * width, hs, width, lane);
-            const float u = dot_row(wu + (size_t)j * width, hs, width, lane);
-            v = fn(g, u);
+            v = gated ? fn(g, dot_row(wu + (size_t)j * width, hs, width, lane)) : fn.single(g);
         }
         if (lane == 0) act[((size_t)t * top + k) * ff + j] = from_f32<T>(v);
     }
@@ -111,7 +122,8 @@ template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, const int* __restrict__ table, int vocab,
                       int top, int experts, const T* __restrict__ down, const T* __restrict__ base, int base_stride,
-                      float weight, const float* __restrict__ weights, T* __restrict__ out, int width, int ff) {
+                      float weight, const float* __restrict__ weights, const float* __restrict__ base_gate, int base_gate_stride,
+                      T* __restrict__ out, int width, int ff) {
     extern __shared__ float as[];                       // [top][ff]
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,7 +142,7 @@ moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, co
         }
         if (lane == 0) {
             float v = weights ? sum : sum * weight;
-            if (base) v += to_f32(base[(size_t)t * base_stride + i]);
+            if (base) v += to_f32(base[(size_t)t * base_stride + i]) * (base_gate ? 1.f / (1.f + expf(-base_gate[(size_t)t * base_gate_stride])) : 1.f);
             out[(size_t)t * width + i] = from_f32<T>(v);
         }
     }
@@ -160,16 +172,17 @@ extern "C" int cib_moe_table_gate_up(const void* h, int h_stride, int dtype, con
 
 extern "C" int cib_moe_table_down(const void* act, int dtype, const int* ids, const int* table, int vocab, int top,
                                   int experts, const void* down, const void* base, int base_stride, float weight,
-                                  const float* weights, void* out, int num_tokens, int width, int ff, cudaStream_t stream) {
+                                  const float* weights, const float* base_gate, int base_gate_stride, void* out, int num_tokens,
+                                  int width, int ff, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
     CIB_REQUIRE((size_t)top * ff <= 12 * 1024, "moe_table: %d x %d activations too large for this kernel", top, ff);
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens, (width + kMoeOutsPerBlock - 1) / kMoeOutsPerBlock);
     const size_t smem = (size_t)top * ff * sizeof(float);
     if (dtype == kF32)
-        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, (float*)out, width, ff);
+        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, base_gate, base_gate_stride, (float*)out, width, ff);
     else if (dtype == kBF16)
-        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, weights, (__nv_bfloat16*)out, width, ff);
+        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, weights, base_gate, base_gate_stride, (__nv_bfloat16*)out, width, ff);
     else
         CIB_REQUIRE(false, "moe_table: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("moe_table_down");
@@ -240,7 +253,8 @@ moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int
 
 // out[r, n] for the rows r of one tile of one expert's group; w: [E][N_total][K] with the expert's rows `w_expert`
 // elements apart.  GATED: columns j and N + j of the expert are gate and up, out[r, j] = silu(gate) * up, out has N
-// columns.  Otherwise out[r, j] for 128 columns a CTA.  `gather`: row r of A is a[(gather[r] / top)]; else a[r].
+// columns.  Otherwise out[r, j] for 128 columns a CTA, through `fn.single` (an expert without a gate squares its ReLU
+// there; the second product passes kind -1).  `gather`: row r of A is a[(gather[r] / top)]; else a[r].
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __restrict__ gather, int top,
@@ -349,8 +363,9 @@ moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int*
 #pragma unroll
                 for (int nt = 0; nt < kGN / 8; ++nt) {
                     const int col = n0 + h * kGN + nt * 8 + quad * 2;
-                    if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[h][nt][2 * hrow], acc[h][nt][2 * hrow + 1]);
-                    else if (col < N) dst[col] = __float2bfloat16_rn(acc[h][nt][2 * hrow]);
+                    const float v0 = fn.single(acc[h][nt][2 * hrow]), v1 = fn.single(acc[h][nt][2 * hrow + 1]);
+                    if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
+                    else if (col < N) dst[col] = __float2bfloat16_rn(v0);
                 }
         }
     }
@@ -358,8 +373,10 @@ moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int*
 
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_pos, int top,
                                    const __nv_bfloat16* __restrict__ base, int base_stride, float weight,
-                                   const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int width) {
+                                   const float* __restrict__ weights, const float* __restrict__ base_gate, int base_gate_stride,
+                                   __nv_bfloat16* __restrict__ out, int width) {
     const int t = blockIdx.x;
+    const float bg = base && base_gate ? 1.f / (1.f + expf(-base_gate[(size_t)t * base_gate_stride])) : 1.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -367,7 +384,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
             if (at >= 0) sum += (weights ? weights[t * top + k] : 1.f) * __bfloat162float(y[(size_t)at * width + i]);
         }
         float v = weights ? sum : sum * weight;
-        if (base) v += __bfloat162float(base[(size_t)t * base_stride + i]);
+        if (base) v += __bfloat162float(base[(size_t)t * base_stride + i]) * bg;
         out[(size_t)t * width + i] = __float2bfloat16_rn(v);
     }
 }
@@ -388,8 +405,9 @@ extern "C" long long cib_moe_table_grouped_workspace_ints(int num_tokens, int to
 // bfloat16 only.  act: [T * top, ff] and y: [T * top, width] scratch rows; ints: see above.
 extern "C" int cib_moe_table_grouped(const void* h, int h_stride, const int* ids, const int* table, int vocab, int top,
                                      int experts, const void* gate_up, const void* down, const void* base, int base_stride,
-                                     float weight, const float* weights, void* out, void* act, void* y, int* ints,
-                                     int num_tokens, int width, int ff, int act_kind, float limit, cudaStream_t stream) {
+                                     float weight, const float* weights, const float* base_gate, int base_gate_stride, void* out,
+                                     void* act, void* y, int* ints, int num_tokens, int width, int ff, int act_kind, float limit,
+                                     cudaStream_t stream) {
     using namespace cib;
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && vocab > 0, "moe_table_grouped: bad sizes");
     CIB_REQUIRE(cib_moe_table_grouped_supports(width, ff, experts), "moe_table_grouped: width %d / ff %d / %d experts are not taken", width, ff, experts);
@@ -409,18 +427,26 @@ extern "C" int cib_moe_table_grouped(const void* h, int h_stride, const int* ids
                                                                                    slot_pos, offsets, tile_expert, tile_row0,
                                                                                    num_tiles, max_tiles);
     CIB_LAUNCH_CHECK("moe_route");
-    dim3 g1(max_tiles, (ff + kGN - 1) / kGN);
-    moe_grouped_gemm_kernel<true><<<g1, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, sorted_slot, top,
-                                                          (const __nv_bfloat16*)gate_up, (long long)2 * ff * width,
-                                                          (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width, ExpertAct{act_kind, limit});
+    const ExpertAct fn{act_kind, limit};
+    if (fn.gated()) {
+        dim3 g1(max_tiles, (ff + kGN - 1) / kGN);
+        moe_grouped_gemm_kernel<true><<<g1, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, sorted_slot, top,
+                                                              (const __nv_bfloat16*)gate_up, (long long)2 * ff * width,
+                                                              (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width, fn);
+    } else {
+        dim3 g1(max_tiles, (ff + 2 * kGN - 1) / (2 * kGN));
+        moe_grouped_gemm_kernel<false><<<g1, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, sorted_slot, top,
+                                                               (const __nv_bfloat16*)gate_up, (long long)ff * width,
+                                                               (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width, fn);
+    }
     CIB_LAUNCH_CHECK("moe_grouped_gate_up");
     dim3 g2(max_tiles, (width + 2 * kGN - 1) / (2 * kGN));
     moe_grouped_gemm_kernel<false><<<g2, 128, 0, stream>>>((const __nv_bfloat16*)act, ff, nullptr, top, (const __nv_bfloat16*)down,
                                                            (long long)width * ff, (__nv_bfloat16*)y, width, offsets, tile_expert,
-                                                           tile_row0, num_tiles, width, ff, ExpertAct{0, 0.f});
+                                                           tile_row0, num_tiles, width, ff, ExpertAct{-1, 0.f});
     CIB_LAUNCH_CHECK("moe_grouped_down");
     moe_combine_kernel<<<num_tokens, 256, 0, stream>>>((const __nv_bfloat16*)y, slot_pos, top, (const __nv_bfloat16*)base, base_stride,
-                                                       weight, weights, (__nv_bfloat16*)out, width);
+                                                       weight, weights, base_gate, base_gate_stride, (__nv_bfloat16*)out, width);
     CIB_LAUNCH_CHECK("moe_combine");
     return 0;
 }

@@ -71,18 +71,18 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_sandwich_layernorm": [_P, _P, _I, _P, _P, _F, _P, _P, _P, _F, _I, _P, _I, _I, _I, _P],
         "cib_relu_squared": [_P, _P, _I, ctypes.c_longlong, _P],
         "cib_sigmoid_gate": [_P, _I, _P, _I, _P, _I, _I, _I, _P],
-        "cib_latent_prep": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, ctypes.c_longlong, _P, _I, _I, _P],
-        "cib_latent_attention_generic": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _I,
+        "cib_latent_prep": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _F, _P, _P, ctypes.c_longlong, _P, _I, _I, _P],
+        "cib_latent_attention_generic": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _F, _P, _I,
                                          _I, _I, _I, _I, _F, _I, _P],
         "cib_latent_attention_mma": [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P, _I, _P, _I, _I, _I, _I,
-                                     _F, _I, _P],
+                                     _F, _I, _F, _I, _P],
         "cib_gemm_generic_batched": [_P, _I, ctypes.c_longlong, _P, _I, ctypes.c_longlong, _I, _P, _I, ctypes.c_longlong, _I,
                                      _I, _I, _I, _I, _P],
         "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
-        "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
-        "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _I, _I, _P],
+        "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+        "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _I, _I, _I, _P],
         "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I,
-                                      _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+                                      _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _F, _P],
         "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _P, _P],
         "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P],
         "cib_hyper_stream": [_P, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _P],
@@ -92,6 +92,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
         "cib_head_rms_gate": [_P, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _I, _I, _P],
         "cib_router_topk": [_P, _I, _I, _I, _P, _P, _I, _P],
+        "cib_router_scored_topk": [_P, _I, _I, _I, _P, _I, _I, _F, _P, _P, _I, _P],
         "cib_rms_stream": [_P, _P, _I, _P, _I, _F, _P, _I, _F, _P, _P, _I, _I, _I, _P],
         "cib_gelu_tanh": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _P],
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
@@ -353,14 +354,22 @@ def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
 
 def latent_prep(proj: torch.Tensor, q_off: int, rq: int, kv_off: int, rk: int, dr: int, q_gain: torch.Tensor,
                 kv_gain: torch.Tensor, eps: float, positions: torch.Tensor, freq: torch.Tensor | None, rot_dims: int,
-                slot_mapping: torch.Tensor | None, cache: torch.Tensor | None, cq_out: torch.Tensor) -> None:
+                slot_mapping: torch.Tensor | None, cache: torch.Tensor | None, cq_out: torch.Tensor | None,
+                rot_gain: float = 1.0) -> None:
     """Per token of the stacked down-projection rows ``proj``: RMS norm of the query latent (columns q_off..+rq) into
-    ``cq_out``; RMS norm of the key/value latent (kv_off..+rk) and interleaved rotary encoding of the ``dr`` columns
-    after it, both written to the token's slot of ``cache[page, 0, 0, slot, rk + dr]`` (if a cache is given)."""
+    ``cq_out`` (None, with ``q_gain`` None and ``rq`` 0: the rows hold no query latent); RMS norm of the key/value latent
+    (kv_off..+rk) and interleaved rotary encoding of the ``dr`` columns after it (cosine and sine times ``rot_gain``),
+    both written to the token's slot of ``cache[page, 0, 0, slot, rk + dr]`` (if a cache is given)."""
     T, stride = proj.shape
-    if proj.stride(1) != 1 or cq_out.shape != (T, rq) or cq_out.dtype != proj.dtype or cq_out.stride(1) != 1:
+    if cq_out is None:
+        if rq != 0 or q_gain is not None:
+            raise KernelError("latent_prep: a query latent needs a place for its norm")
+        q_gain = kv_gain
+    elif cq_out.shape != (T, rq) or cq_out.dtype != proj.dtype or cq_out.stride(1) != 1:
         raise KernelError("latent_prep: rows do not fit")
-    if q_gain.numel() != rq or kv_gain.numel() != rk or q_gain.dtype != kv_gain.dtype:
+    if proj.stride(1) != 1:
+        raise KernelError("latent_prep: rows do not fit")
+    if (cq_out is not None and q_gain.numel() != rq) or kv_gain.numel() != rk or q_gain.dtype != kv_gain.dtype:
         raise KernelError("latent_prep: gains do not fit the latents")
     slots = 0
     if cache is not None:
@@ -373,9 +382,11 @@ def latent_prep(proj: torch.Tensor, q_off: int, rq: int, kv_off: int, rk: int, d
         _cuda(proj, "proj", contiguous=False), _code(proj, "proj"), proj.stride(0), q_off, rq, kv_off, rk, dr,
         _cuda(q_gain, "q_gain"), _cuda(kv_gain, "kv_gain"), _code(q_gain, "q_gain"), float(eps),
         _cuda(positions, "positions", torch.int32), _cuda(freq, "freq", torch.float32) if freq is not None else None,
-        rot_dims if freq is not None else 0, _cuda(slot_mapping, "slot_mapping", torch.int32) if cache is not None else None,
-        _cuda(cache, "cache") if cache is not None else None, slots, _cuda(cq_out, "cq_out", contiguous=False),
-        cq_out.stride(0), T, _stream())
+        rot_dims if freq is not None else 0, float(rot_gain),
+        _cuda(slot_mapping, "slot_mapping", torch.int32) if cache is not None else None,
+        _cuda(cache, "cache") if cache is not None else None, slots,
+        _cuda(cq_out, "cq_out", contiguous=False) if cq_out is not None else None,
+        cq_out.stride(0) if cq_out is not None else 0, T, _stream())
     _check(rc, "latent_prep")
     _count()
 
@@ -384,10 +395,11 @@ def latent_attention_generic(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Te
                              block_table: torch.Tensor, query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
                              token_request: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor | None, rot_dims: int,
                              sinks: torch.Tensor | None, num_heads: int, dn: int, rk: int, dr: int, scale: float,
-                             window: int = 0) -> None:
+                             window: int = 0, rot_gain: float = 1.0) -> None:
     """Causal multi-query attention over cached latent rows ``[c | k_rot]``: ``q_abs[T, H*rk]`` are the queries with the
     key up-projection folded in, ``q[T, H*(dn+dr)]`` holds each head's rotary part (encoded by the kernel), ``out[T, H*rk]``
-    the weighted sums of the latents.  ``sinks[H]``: per-head scores that only join the softmax denominator."""
+    the weighted sums of the latents.  ``sinks[H]``: per-head scores that only join the softmax denominator.
+    ``window`` w > 0: query i sees key j only when ``i - j < w``; ``rot_gain``: a factor on the rotation's cosine and sine."""
     T = q.shape[0]
     if q_abs.shape != (T, num_heads * rk) or out.shape != (T, num_heads * rk) or q.shape[1] != num_heads * (dn + dr):
         raise KernelError("latent_attention: q_abs / q / out do not fit the sizes")
@@ -403,7 +415,7 @@ def latent_attention_generic(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Te
         cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32), block_table.stride(0),
         _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
         _cuda(token_request, "token_request", torch.int32), _cuda(positions, "positions", torch.int32),
-        _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
+        _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0, float(rot_gain),
         _cuda(sinks, "sinks") if sinks is not None else None, _code(sinks, "sinks") if sinks is not None else 0,
         T, num_heads, rk, dr, float(scale), int(window), _stream())
     _check(rc, "latent_attention_generic")
@@ -427,9 +439,8 @@ def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor
                          block_table: torch.Tensor, query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
                          query_lens: list, freq: torch.Tensor | None, rot_dims: int, sinks: torch.Tensor | None,
                          num_heads: int, dn: int, rk: int, dr: int, scale: float, max_seq_len: int,
-                         decode_only: bool = False) -> None:
-    """The bfloat16 tensor-core form of :func:`latent_attention_generic` (same operands, ``q_abs`` in bfloat16; no
-    window).  ``query_lens``: tokens per request as host integers, an upper bound in a captured step (CTAs that find
+                         decode_only: bool = False, window: int = 0, rot_gain: float = 1.0) -> None:
+    """The bfloat16 tensor-core form of :func:`latent_attention_generic` (same operands, ``q_abs`` in bfloat16).  ``query_lens``: tokens per request as host integers, an upper bound in a captured step (CTAs that find
     no request leave); ``max_seq_len``: the longest context, which decides how a decode step's keys are split;
     ``decode_only``: every request brings one token (query tiles of 32 rows then, when the heads fit)."""
     T = q.shape[0]
@@ -448,7 +459,9 @@ def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor
     tile_rows = 32 if decode_only and num_heads <= 32 else 64
     tiles = lib.cib_latent_attention_mma_tiles(lens, len(query_lens), num_heads, tile_rows)
     head_blocks = -(-num_heads // 64) if num_heads > 64 else 1
-    splits = latent_attention_splits(tiles, head_blocks, max_seq_len)
+    # with a window a query tile reads at most the window and its own tokens' keys
+    reach = min(max_seq_len, window + tile_rows) if window else max_seq_len
+    splits = latent_attention_splits(tiles, head_blocks, reach)
     scratch = torch.empty(T * num_heads * splits * (rk + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     rc = lib.cib_latent_attention_mma(
         _cuda(q_abs, "q_abs", contiguous=False), q_abs.stride(0), _cuda(q, "q", contiguous=False), q.stride(0), dn,
@@ -456,7 +469,8 @@ def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
         R, tiles, tile_rows, _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
-        _cuda(sinks, "sinks") if sinks is not None else None, T, num_heads, rk, dr, float(scale), splits, _stream())
+        _cuda(sinks, "sinks") if sinks is not None else None, T, num_heads, rk, dr, float(scale), splits, float(rot_gain),
+        int(window), _stream())
     _check(rc, "latent_attention_mma")
     _count()
     if splits > 1:
@@ -656,17 +670,22 @@ MOE_GROUPED_MIN_ROWS = 128
 
 def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: torch.Tensor, gate_up: torch.Tensor,
                            down: torch.Tensor, base: torch.Tensor | None, out: torch.Tensor,
-                           weights: torch.Tensor | None = None, clamp_limit: float | None = None) -> None:
+                           weights: torch.Tensor | None = None, clamp_limit: float | None = None, activation: str | None = None,
+                           base_gate: torch.Tensor | None = None) -> None:
     """out[t] = base[t] + (1/top) * sum over k of expert(table[ids[t], k])(h[t]) with gated experts
     (``ids`` None: the table has a row per row of ``h`` — experts chosen by a router; ``weights`` float32 [T, top]:
     a weight per choice instead of 1/top; ``clamp_limit``: the experts' activation is
     ``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``)
     ``down_e(silu(gate_e h) * up_e h)``; ``gate_up[E, 2 ff, W]`` (gate rows first), ``down[E, W, ff]``, ``table[V, top]``.
+    ``activation="relu2"``: experts without a gate, ``down_e(relu(up_e h) ** 2)``, whose first matrix is ``[E, ff, W]``.
+    ``base_gate`` float32 [T] (any stride): ``base[t]`` is multiplied by ``sigmoid(base_gate[t])`` as it is added.
     Few rows, 32-bit, or sizes that are not multiples of 32: two launches (a matrix-vector product per token and
     choice).  Many bfloat16 rows: grouped by expert (see ``MOE_GROUPED_MIN_ROWS``)."""
     T, W = h.shape
+    if activation not in (None, "relu2"):
+        raise KernelError(f"moe_table: activation {activation!r} is not one of the experts' forms")
     E, two_ff, W2 = gate_up.shape
-    ff = two_ff // 2
+    ff = two_ff if activation == "relu2" else two_ff // 2
     V, top = table.shape
     if W2 != W or down.shape != (E, W, ff) or out.shape != (T, W) or not (h.dtype == gate_up.dtype == down.dtype == out.dtype):
         raise KernelError("moe_table: weights, rows and out do not fit")
@@ -679,6 +698,12 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: tor
     p_ids = _cuda(ids, "ids", torch.int32) if ids is not None else None
     p_w = _cuda(weights, "weights", torch.float32) if weights is not None else None
     act_kind, limit = (1, float(clamp_limit)) if clamp_limit is not None else (0, 0.0)
+    if activation == "relu2":
+        act_kind, limit = 2, 0.0
+    if base_gate is not None and (base is None or base_gate.shape != (T,)):
+        raise KernelError("moe_table: a gate for base needs base and one number per row")
+    p_bg = _cuda(base_gate, "base_gate", torch.float32, contiguous=False) if base_gate is not None else None
+    bg_stride = base_gate.stride(0) if base_gate is not None else 0
     lib = library()
     if (h.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_MIN_ROWS and h.stride(0) % 8 == 0
             and lib.cib_moe_table_grouped_supports(W, ff, E)):
@@ -689,7 +714,7 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: tor
         rc = lib.cib_moe_table_grouped(
             _cuda(h, "h", contiguous=False), h.stride(0), p_ids, _cuda(table, "table", torch.int32), V, top, E,
             _cuda(gate_up, "gate_up"), _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
-            base.stride(0) if base is not None else 0, 1.0 / top, p_w, _cuda(out, "out"), _cuda(act, "act"), _cuda(y, "y"),
+            base.stride(0) if base is not None else 0, 1.0 / top, p_w, p_bg, bg_stride, _cuda(out, "out"), _cuda(act, "act"), _cuda(y, "y"),
             _cuda(ints, "ints"), T, W, ff, act_kind, limit, _stream())
         _check(rc, "moe_table_grouped")
         for _ in range(4):
@@ -702,7 +727,7 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: tor
     _check(rc, "moe_table_gate_up")
     rc = lib.cib_moe_table_down(_cuda(act, "act"), _code(act, "act"), p_ids, _cuda(table, "table", torch.int32),
                                 V, top, E, _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
-                                base.stride(0) if base is not None else 0, 1.0 / top, p_w, _cuda(out, "out"), T, W, ff, _stream())
+                                base.stride(0) if base is not None else 0, 1.0 / top, p_w, p_bg, bg_stride, _cuda(out, "out"), T, W, ff, _stream())
     _check(rc, "moe_table_down")
     _count()
     _count()
@@ -1008,6 +1033,25 @@ def router_topk(logits: torch.Tensor, top: int, choice: torch.Tensor, weight: to
     _count()
 
 
+def router_scored_topk(logits: torch.Tensor, top: int, choice: torch.Tensor, weight: torch.Tensor, *,
+                       correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1, scale: float = 1.0) -> None:
+    """From float32 logits [T, E] with scores ``s = sigmoid(logits)``: ``choice`` int32 [T, top], the experts with the
+    largest ``s + correction`` (float32 [E], None: no correction; the lower index wins a tie) among the ``keep`` of
+    ``groups`` equal groups of neighbouring experts whose two largest ``s + correction`` sum highest; ``weight`` float32
+    [T, top] = ``scale * s`` of the chosen, not renormalised."""
+    T, E = logits.shape
+    if choice.shape != (T, top) or weight.shape != (T, top) or logits.stride(1) != 1:
+        raise KernelError("router_scored_topk: shapes do not fit")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+        raise KernelError("router_scored_topk: the correction must be float32 with a number per expert")
+    rc = library().cib_router_scored_topk(_cuda(logits, "logits", torch.float32, contiguous=False), logits.stride(0), E, top,
+                                          _cuda(correction, "correction") if correction is not None else None, int(groups),
+                                          int(keep), float(scale), _cuda(choice, "choice", torch.int32),
+                                          _cuda(weight, "weight", torch.float32), T, _stream())
+    _check(rc, "router_scored_topk")
+    _count()
+
+
 # ---- attention with a capped score and a window that keeps the first tokens ---------------------------------------------------
 
 def _f32_vec(t: torch.Tensor | None, n: int, what: str):
@@ -1024,16 +1068,20 @@ def window_attention_prep(qkv: torch.Tensor, positions: torch.Tensor, slot_mappi
                           vdim: int, v_first: torch.Tensor | None, mix: torch.Tensor | None, cache: torch.Tensor | None, *,
                           bias: torch.Tensor | None = None, norm: bool = True, q_gain: torch.Tensor | None = None,
                           k_gain: torch.Tensor | None = None, norm_first: bool = False, rot_half: bool = False,
-                          q_temp: tuple | None = None) -> None:
+                          q_temp: tuple | None = None, value_from_key: bool = False, rot_gain: float = 1.0) -> None:
     """On the packed rows ``[q | k | v]``: ``bias`` (float32, one value per column) is added; rotary encoding of the
     first ``rot_dims`` values of every query and key head (32-bit angle ``pos * freq[i]``; neighbouring pairs, or with
     ``rot_half`` the pairs (i, i + rot_dims / 2)); with ``norm`` every query and key head is divided by its root mean
     square and multiplied by ``q_gain`` / ``k_gain`` (float32 [dim], None: no gain), after the rotation or, with
     ``norm_first``, before it; ``q_temp = (coef, every)`` multiplies the queries by
-    ``1 + coef * ln(floor((pos + 1) / every) + 1)``.  Queries are rewritten in place; keys and values
+    ``1 + coef * ln(floor((pos + 1) / every) + 1)``.  ``value_from_key``: the rows are ``[q | k]`` and a token's value is
+    its key as it stands before norm and rotation (``vdim == dim``).  ``rot_gain``: a factor on the rotation's cosine and
+    sine.  Queries are rewritten in place; keys and values
     (``(1 - mix) * v + mix * v_first`` when both are given) go to ``cache[page, 0, kv head, slot, dim + vdim]``."""
     T, stride = qkv.shape
-    columns = (num_heads + num_kv_heads) * dim + num_kv_heads * vdim
+    columns = (num_heads + num_kv_heads) * dim + (0 if value_from_key else num_kv_heads * vdim)
+    if value_from_key and (vdim != dim or v_first is not None):
+        raise KernelError("window_attention_prep: values taken from the keys have the keys' size and are not mixed")
     if stride < columns or qkv.stride(1) != 1:
         raise KernelError("window_attention_prep: rows are too short")
     if cache is not None:
@@ -1056,7 +1104,7 @@ def window_attention_prep(qkv: torch.Tensor, positions: torch.Tensor, slot_mappi
         cache.shape[3] if cache is not None else 1, T,
         _f32_vec(bias, columns, "bias"), _f32_vec(q_gain, dim, "q_gain"), _f32_vec(k_gain, dim, "k_gain"), 1 if norm else 0,
         1 if norm_first else 0, 1 if rot_half else 0, 1 if q_temp else 0, float(q_temp[0]) if q_temp else 0.0,
-        int(q_temp[1]) if q_temp else 1, _stream())
+        int(q_temp[1]) if q_temp else 1, 1 if value_from_key else 0, float(rot_gain), _stream())
     _check(rc, "window_attention_prep")
     _count()
 

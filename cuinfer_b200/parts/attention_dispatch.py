@@ -54,25 +54,26 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: Step
 _FORCE_GENERIC_LATENT = os.environ.get("CUINFER_B200_LATENT_ATTENTION", "") == "generic"
 
 
-def latent_tensor_cores(dtype: torch.dtype, rk: int, dr: int, dn: int, window: int) -> bool:
+def latent_tensor_cores(dtype: torch.dtype, rk: int, dr: int, dn: int) -> bool:
     """Whether attention over cached latents runs on the tensor-core kernel (bfloat16, latent and rotary sizes in
-    multiples of 16, no window); else the all-sizes kernel, which is also the 32-bit path.  The query-side product
+    multiples of 16; with or without a window); else the all-sizes kernel, which is also the 32-bit path.  The query-side product
     then delivers bfloat16 operands instead of 32-bit ones.  ``CUINFER_B200_LATENT_ATTENTION=generic`` keeps everything
     on the all-sizes kernel (for comparisons)."""
-    return (dtype == torch.bfloat16 and not window and not _FORCE_GENERIC_LATENT
+    return (dtype == torch.bfloat16 and not _FORCE_GENERIC_LATENT
             and kernels.latent_attention_mma_supports(rk, dr, dn))
 
 
 def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, freq, rot_dims: int,
-                     sinks, num_heads: int, dn: int, rk: int, dr: int, scale: float, window: int) -> None:
+                     sinks, num_heads: int, dn: int, rk: int, dr: int, scale: float, window: int, rot_gain: float = 1.0) -> None:
     """Attention of the step's rows over cached latent rows; ``q_abs`` bfloat16 selects the tensor-core kernel."""
-    if q_abs.dtype == torch.bfloat16 and latent_tensor_cores(q.dtype, rk, dr, dn, window) and q_abs.stride(0) % 8 == 0:
+    if q_abs.dtype == torch.bfloat16 and latent_tensor_cores(q.dtype, rk, dr, dn) and q_abs.stride(0) % 8 == 0:
         kernels.latent_attention_mma(q_abs, q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                      ctx.query_lens_for_launch(), freq, rot_dims, sinks, num_heads, dn, rk, dr, scale,
-                                     max(1, ctx.max_seq_len), decode_only=ctx.decode_only)
+                                     max(1, ctx.max_seq_len), decode_only=ctx.decode_only, window=window, rot_gain=rot_gain)
         return
     kernels.latent_attention_generic(q_abs, q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
-                                     ctx.token_request, ctx.positions, freq, rot_dims, sinks, num_heads, dn, rk, dr, scale, window)
+                                     ctx.token_request, ctx.positions, freq, rot_dims, sinks, num_heads, dn, rk, dr, scale, window,
+                                     rot_gain=rot_gain)
 
 
 def window_decode_splits(ctx: StepContext, num_kv_heads: int, window: int, keep_first: int) -> int:

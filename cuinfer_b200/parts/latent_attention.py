@@ -18,9 +18,18 @@ their first ``kv_rank`` columns, then ``Uv_h`` on the result (again a batch).  S
   one stacked projection [Dq; Dkv; G] -> norms + rotary + cache write (one kernel) -> Uq -> q_abs (batched) ->
   attention -> Uv (batched) -> gate -> O.
 
+Variants, each a parameter of the spec:
+
+* ``q_rank`` absent or 0: the queries have no latent, ``q = Q h`` with one matrix (role ``q``);
+* ``window`` w: the query at position i sees key j only when ``0 <= i - j < w`` (pages behind the window are given back);
+* ``own_cache=False``: the layer has no ``Dkv`` (and no norm for it): it reads the rows ``[c | rot(k_r)]`` that an earlier
+  layer cached (``ModelSpec.cache_source`` names it), with its own ``Uk``, ``Uv``, queries, window and everything else;
+  ``kv_rank``, ``rot_dim`` and the rotation must be the earlier layer's;
+* a position encoding with a ``magnitude`` multiplies cosine and sine by it, on queries and on the cached key part.
+
 Spec: ``PartSpec("latent_attention", num_heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, eps, sink, gate, window,
-position=PartSpec(...), names={...})``; ``names`` maps the roles (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, g, o) to
-tensor names relative to the mixer's prefix.
+own_cache, position=PartSpec(...), names={...})``; ``names`` maps the roles (dq, dq_norm, uq, q, dkv, dkv_norm, uk, uv, sink,
+g, o) to tensor names relative to the mixer's prefix.
 """
 from __future__ import annotations
 
@@ -37,7 +46,7 @@ from .linear import Linear
 from .registry import MIXERS, POSITION_ENCODINGS
 from .spec import PagedCacheNeed, PartSpec, TensorSpec
 
-_DEFAULT_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
+_DEFAULT_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
                   "uv": "uv", "sink": "sink", "g": "g", "o": "o"}
 
 
@@ -63,7 +72,8 @@ class LatentAttention(Mixer):
         self.dim = int(spec.dim)
         self.rot_dim = int(spec.rot_dim)
         self.vdim = int(spec.vdim)
-        self.q_rank = int(spec.q_rank)
+        self.q_rank = int(spec.get("q_rank") or 0)           # 0: queries projected directly
+        self.own_cache = bool(spec.get("own_cache", True))
         self.kv_rank = int(spec.kv_rank)
         self.eps = float(spec.eps)
         scale = spec.get("scale")
@@ -72,11 +82,11 @@ class LatentAttention(Mixer):
         self.has_gate = bool(spec.get("gate", False))
         window = spec.get("window")
         self.window = int(window) if window else 0
-        for name in ("num_heads", "dim", "vdim", "q_rank", "kv_rank"):
+        for name in ("num_heads", "dim", "vdim", "kv_rank"):
             if getattr(self, name) <= 0:
                 raise ValueError(f"latent_attention: {name} must be positive")
-        if self.rot_dim < 0:
-            raise ValueError("latent_attention: rot_dim must not be negative")
+        if self.rot_dim < 0 or self.q_rank < 0:
+            raise ValueError("latent_attention: rot_dim and q_rank must not be negative")
         pos_spec: PartSpec = spec.get("position") or PartSpec("none")
         self.position = POSITION_ENCODINGS.get(pos_spec.kind)(pos_spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         if self.position.rotary_dim > self.rot_dim:
@@ -90,10 +100,19 @@ class LatentAttention(Mixer):
         self.q_size = H * (self.dim + self.rot_dim)
         self.v_size = H * self.vdim
         self.row = self.kv_rank + self.rot_dim                     # what a token keeps in the cache
-        down_names = [self.names["dq"], self.names["dkv"]] + ([self.names["g"]] if self.has_gate else [])
-        down_sizes = [self.q_rank, self.row] + ([self.v_size] if self.has_gate else [])
+        # one stacked projection of the mixer's input: [query latent, or the queries themselves | Dkv | G]
+        self.q_cols = self.q_rank or self.q_size
+        down_names = [self.names["dq"] if self.q_rank else self.names["q"]]
+        down_sizes = [self.q_cols]
+        if self.own_cache:
+            down_names.append(self.names["dkv"])
+            down_sizes.append(self.row)
+        if self.has_gate:
+            down_names.append(self.names["g"])
+            down_sizes.append(self.v_size)
         self.down = Linear(down_names, down_sizes, hidden_size, dtype)
-        self.uq = Linear([self.names["uq"]], [self.q_size], self.q_rank, dtype)
+        self.uq = Linear([self.names["uq"]], [self.q_size], self.q_rank, dtype) if self.q_rank else None
+        self.rot_gain = float(getattr(self.position, "magnitude", 1.0))
         self.o = Linear([self.names["o"]], [hidden_size], self.v_size, dtype)
         self.uk_t: Optional[torch.Tensor] = None     # [H, kv_rank, dim]: Uk per head, transposed for the query side
         self.uv: Optional[torch.Tensor] = None       # [H, vdim, kv_rank]
@@ -105,25 +124,30 @@ class LatentAttention(Mixer):
     def _own_specs(self) -> Dict[str, TensorSpec]:
         n, H = self.names, self.num_heads
         out = {
-            "dq_norm": TensorSpec(n["dq_norm"], (self.q_rank,), keep_stored_precision=True, init="ones"),
-            "dkv_norm": TensorSpec(n["dkv_norm"], (self.kv_rank,), keep_stored_precision=True, init="ones"),
             "uk": TensorSpec(n["uk"], (H * self.dim, self.kv_rank)),
             "uv": TensorSpec(n["uv"], (H * self.vdim, self.kv_rank)),
         }
+        if self.q_rank:
+            out["dq_norm"] = TensorSpec(n["dq_norm"], (self.q_rank,), keep_stored_precision=True, init="ones")
+        if self.own_cache:
+            out["dkv_norm"] = TensorSpec(n["dkv_norm"], (self.kv_rank,), keep_stored_precision=True, init="ones")
         if self.has_sink:
             out["sink"] = TensorSpec(n["sink"], (H,), keep_stored_precision=True, init="zeros")
         return out
 
     def tensors(self) -> List[TensorSpec]:
-        return self.down.tensors() + self.uq.tensors() + self.o.tensors() + list(self._own_specs().values()) + self.position.tensors()
+        return (self.down.tensors() + (self.uq.tensors() if self.uq else []) + self.o.tensors()
+                + list(self._own_specs().values()) + self.position.tensors())
 
     def load(self, store) -> None:
         self.down.load(store)
-        self.uq.load(store)
+        if self.uq:
+            self.uq.load(store)
         self.o.load(store)
         own = self._own_specs()
-        self.q_gain, self.kv_gain = store.get(own["dq_norm"]), store.get(own["dkv_norm"])
-        if self.q_gain.dtype != self.kv_gain.dtype:
+        self.q_gain = store.get(own["dq_norm"]) if self.q_rank else None
+        self.kv_gain = store.get(own["dkv_norm"]) if self.own_cache else None
+        if self.q_gain is not None and self.kv_gain is not None and self.q_gain.dtype != self.kv_gain.dtype:
             self.q_gain, self.kv_gain = self.q_gain.float(), self.kv_gain.float()
         H = self.num_heads
         uk = store.get(own["uk"]).to(self.dtype)
@@ -145,7 +169,7 @@ class LatentAttention(Mixer):
     def workspace_bytes(self, tokens: int) -> int:
         width = 2 if self.dtype == torch.bfloat16 else 4
         H = self.num_heads
-        values = (self.down.workspace_bytes(tokens) + self.uq.workspace_bytes(tokens) + self.o.workspace_bytes(tokens)
+        values = (self.down.workspace_bytes(tokens) + (self.uq.workspace_bytes(tokens) if self.uq else 0) + self.o.workspace_bytes(tokens)
                   + tokens * (self.q_rank + H * self.kv_rank + 2 * self.v_size) * width + tokens * H * self.kv_rank * 4)
         return values
 
@@ -154,24 +178,32 @@ class LatentAttention(Mixer):
         kv = ctx.paged_kv(run)
         T = x.shape[0]
         H, rk, dr, dn = self.num_heads, self.kv_rank, self.rot_dim, self.dim
-        down = self.down.forward(x)                                          # [T, q_rank | kv_rank + rot_dim | H vdim]
+        if kv.writes != self.own_cache:
+            raise RuntimeError("latent_attention: a layer with its own down-projection writes its cache, one without reads another's")
+        down = self.down.forward(x)                        # [T, q_rank or H (dim + rot_dim) | kv_rank + rot_dim | H vdim]
         freq = self.position.frequencies() if self.position.rotary_dim else None
-        cq = torch.empty((T, self.q_rank), dtype=down.dtype, device=down.device)
-        kernels.latent_prep(down, 0, self.q_rank, self.q_rank, rk, dr, self.q_gain, self.kv_gain, self.eps, ctx.positions,
-                            freq, self.position.rotary_dim, kv.group.slot_mapping if kv.writes else None,
-                            kv.cache if kv.writes else None, cq)
-        q = self.uq.forward(cq)                                              # [T, H (dim + rot_dim)]
+        if self.q_rank:
+            cq = torch.empty((T, self.q_rank), dtype=down.dtype, device=down.device)
+            kernels.latent_prep(down, 0, self.q_rank, self.q_rank, rk, dr, self.q_gain, self.kv_gain, self.eps, ctx.positions,
+                                freq, self.position.rotary_dim, kv.group.slot_mapping if kv.writes else None,
+                                kv.cache if kv.writes else None, cq, rot_gain=self.rot_gain)
+            q = self.uq.forward(cq)                                          # [T, H (dim + rot_dim)]
+        else:
+            if self.own_cache:
+                kernels.latent_prep(down, 0, 0, self.q_cols, rk, dr, None, self.kv_gain, self.eps, ctx.positions, freq,
+                                    self.position.rotary_dim, kv.group.slot_mapping, kv.cache, None, rot_gain=self.rot_gain)
+            q = down[:, :self.q_size]
         # the tensor-core kernel takes the absorbed queries in bfloat16; the all-sizes kernel keeps them in 32 bits
-        fast = attention_dispatch.latent_tensor_cores(q.dtype, rk, dr, dn, self.window)
+        fast = attention_dispatch.latent_tensor_cores(q.dtype, rk, dr, dn)
         q_abs = torch.empty((T, H * rk), dtype=torch.bfloat16 if fast else torch.float32, device=q.device)
         per_head_products(q.view(T, H, dn + dr)[:, :, :dn].transpose(0, 1), self.uk_t, q_abs.view(T, H, rk).transpose(0, 1))
         latent = torch.empty((T, H * rk), dtype=q.dtype, device=q.device)
         attention_dispatch.latent_attention(q_abs, q, latent, kv, ctx, freq, self.position.rotary_dim, self.sinks,
-                                            H, dn, rk, dr, self.scale, self.window)
+                                            H, dn, rk, dr, self.scale, self.window, rot_gain=self.rot_gain)
         heads = torch.empty((T, self.v_size), dtype=q.dtype, device=q.device)
         per_head_products(latent.view(T, H, rk).transpose(0, 1), self.uv, heads.view(T, H, self.vdim).transpose(0, 1))
         if self.has_gate:
             gated = torch.empty_like(heads)
-            kernels.sigmoid_gate(heads, down[:, self.q_rank + self.row:], gated)
+            kernels.sigmoid_gate(heads, down[:, self.q_cols + (self.row if self.own_cache else 0):], gated)
             heads = gated
         return self.o.forward(heads)

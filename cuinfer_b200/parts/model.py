@@ -7,6 +7,7 @@ the final norm and the output projection, with the head aliasing the embedding w
 """
 from __future__ import annotations
 
+from dataclasses import replace
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -99,7 +100,9 @@ class DecoderModel:
         return list(enumerate(self.order))
 
     def cache_needs(self) -> Dict[int, PagedCacheNeed]:
-        """Paged cache of every run that owns one (runs that read another run's cache are left out)."""
+        """Paged cache of every run that owns one (runs that read another run's cache are left out).  A run whose cache
+        is read by a run that looks further back keeps its tokens for as long as that reader needs them: its window
+        becomes the widest of its readers' (none, if a reader has none)."""
         out: Dict[int, PagedCacheNeed] = {}
         for run, layer in self.runs():
             need = self.blocks[layer].mixer.cache_need()
@@ -111,6 +114,13 @@ class DecoderModel:
                 src_need = self.blocks[self.order[self.cache_source[run]]].mixer.cache_need()
                 if src_need is None or (src_need.num_kv_heads, src_need.head_dim, src_need.planes) != (need.num_kv_heads, need.head_dim, need.planes):
                     raise ValueError(f"run {run} cannot read run {self.cache_source[run]}'s cache: shapes differ")
+                src = self.cache_source[run]
+                if src in out:
+                    have = out[src]
+                    if need.window is not None and have.window is not None and (need.chunked, need.keep_first) != (have.chunked, have.keep_first):
+                        raise ValueError(f"run {run} cannot read run {src}'s cache: they keep different tokens")
+                    if have.window is not None and (need.window is None or need.window > have.window):
+                        out[src] = replace(have, window=need.window)
                 continue
             out[run] = need
         return out

@@ -72,7 +72,16 @@ class RotaryInterleaved(PositionEncoding):
     its full-range sine and cosine in 32 bits.  Spec: ``PartSpec("rope_interleaved", theta=..., rotary_dim=...,
     scaling=None)``.  ``scaling = (factor, low, high, original)`` rescales the frequencies by wavelength
     ``l = 2 pi / f`` against a context of ``original`` tokens: kept where ``l < original / high``, divided by ``factor``
-    where ``l > original / low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``."""
+    where ``l > original / low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``.
+
+    ``scaling`` may also be a mapping that names another law:
+
+    * ``{"kind": "linear", "factor": c}``: every frequency is divided by ``c``;
+    * ``{"kind": "ramp", "factor": c, "original": n, "fast": a, "slow": b}``: with
+      ``index(t) = rotary_dim * ln(n / (2 pi t)) / (2 ln theta)`` (the pair whose wave makes ``t`` turns over ``n``
+      positions), ``lo = max(floor(index(a)), 0)``, ``hi = min(ceil(index(b)), rotary_dim - 1)`` and
+      ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair i turns at ``f_i / c * r_i + f_i * (1 - r_i)``, and both
+      cosine and sine are multiplied by ``magnitude = 0.1 ln(c) + 1`` (the kernels take it beside the frequencies)."""
 
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
@@ -81,6 +90,22 @@ class RotaryInterleaved(PositionEncoding):
         if self.rotary_dim < 0 or self.rotary_dim % 2 or not self.theta > 0:
             raise ValueError(f"rope_interleaved: rotary_dim must be even and theta positive, got {self.rotary_dim}, {self.theta}")
         scaling = spec.get("scaling")
+        self.law: Optional[tuple] = None            # ("linear", factor) or ("ramp", factor, original, fast, slow)
+        self.magnitude = 1.0                        # what cosine and sine are multiplied by
+        if isinstance(scaling, dict):
+            kind = scaling.get("kind")
+            if kind == "linear":
+                self.law = ("linear", float(scaling["factor"]))
+            elif kind == "ramp":
+                self.law = ("ramp",) + tuple(float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+                if self.law[2] <= 0 or self.law[3] <= 0 or self.law[4] <= 0 or self.theta == 1.0:
+                    raise ValueError(f"rope: a ramp needs positive original, fast and slow and theta != 1, got {scaling}")
+                self.magnitude = 0.1 * math.log(self.law[1]) + 1.0
+            else:
+                raise ValueError(f"rope: scaling kind {kind!r} is not linear or ramp")
+            if not self.law[1] > 0:
+                raise ValueError(f"rope: the scaling factor must be positive, got {scaling}")
+            scaling = None
         self.scaling = tuple(float(v) for v in scaling) if scaling else None
         if self.scaling is not None and (len(self.scaling) != 4 or self.scaling[0] <= 0 or self.scaling[2] == self.scaling[1]
                                          or self.scaling[1] <= 0 or self.scaling[2] <= 0 or self.scaling[3] <= 0):
@@ -101,6 +126,19 @@ class RotaryInterleaved(PositionEncoding):
             s = (original / wavelength - low) / (high - low)
             blended = (1.0 - s) * f / factor + s * f
             f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blended))
+        if self.law is not None and self.law[0] == "linear":
+            f = f / self.law[1]
+        elif self.law is not None:
+            _, factor, original, fast, slow = self.law
+            dims = self.rotary_dim
+
+            def index_of(turns: float) -> float:
+                return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(index_of(fast)), 0)
+            hi = min(math.ceil(index_of(slow)), dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
         return f.float()
 
     def load(self, store) -> None:
@@ -112,7 +150,7 @@ class RotaryInterleaved(PositionEncoding):
             return None
         if self._freq is None:
             device = torch.device(self._device or "cuda")
-            key = ("interleaved", self.theta, self.rotary_dim, self.scaling, str(device))
+            key = ("interleaved", self.theta, self.rotary_dim, self.scaling, self.law, str(device))
             if key not in _TABLES:
                 _TABLES[key] = self.host_frequencies().to(device)
             self._freq = _TABLES[key]

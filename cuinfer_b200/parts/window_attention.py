@@ -6,7 +6,8 @@ For the mixer's input h, H query heads and G key/value heads (query head i uses 
 and key size ``dim``, value size ``vdim``:
 
 * ``q = Wq h``, ``k = Wk h``, ``v = Wv h``; with ``bias`` each has a bias (the tensor's name plus ``bias_suffix``),
-  added in 32 bits;
+  added in 32 bits; with ``value_from_key`` there is no ``Wv``: a token's value is its key as projected, before norm and
+  rotation (``vdim == dim``);
 * ``qk_norm``: ``"unit"`` divides each head of q and k by its root mean square over ``dim`` (``eps`` inside the root),
   ``"gain"`` also multiplies by a gain of ``dim`` values shared by all heads (one for q, one for k), ``"none"`` leaves
   them; the norm comes after the position encoding or, with ``norm_first``, before it;
@@ -27,7 +28,7 @@ The cache holds a token's key and (mixed) value side by side: ``PagedCacheNeed(G
 keep_first, chunked)``; pages behind the window (before the chunk) are given back, except those of the kept tokens.
 
 Spec: ``PartSpec("window_attention", num_heads, num_kv_heads, dim, vdim, scale, softcap, window, keep_first, chunked,
-qk_norm, norm_first, eps, bias, bias_suffix, q_temp, distance_bias, sink, value_mix, position=PartSpec(...),
+qk_norm, norm_first, eps, bias, bias_suffix, q_temp, distance_bias, sink, value_mix, value_from_key, position=PartSpec(...),
 names=(q, k, v, o, mix, q_norm, k_norm, sink))``.  ``qk_unit_norm`` (True / False) is the older spelling of ``qk_norm``
 ``"unit"`` / ``"none"``.
 """
@@ -87,6 +88,9 @@ class WindowAttention(Mixer):
         self.value_mix = spec.get("value_mix")
         if self.value_mix not in (None, "source", "mixed"):
             raise ValueError(f"window_attention: value_mix must be None, 'source' or 'mixed', got {self.value_mix!r}")
+        self.value_from_key = bool(spec.get("value_from_key", False))
+        if self.value_from_key and (self.vdim != self.dim or self.value_mix):
+            raise ValueError("window_attention: values taken from the keys have the keys' size and are not mixed")
         pos_spec: PartSpec = spec.get("position") or PartSpec("none")
         self.position = POSITION_ENCODINGS.get(pos_spec.kind)(pos_spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         if self.position.rotary_dim > self.dim:
@@ -97,13 +101,17 @@ class WindowAttention(Mixer):
         q, k, v, o, mix, q_norm, k_norm, sink = names + ("q.norm", "k.norm", "sink")[len(names) - 5:]
         p = prefix
         self.q_size, self.k_size, self.v_size = self.num_heads * self.dim, self.num_kv_heads * self.dim, self.num_kv_heads * self.vdim
-        self.qkv = Linear([f"{p}.{q}", f"{p}.{k}", f"{p}.{v}"], [self.q_size, self.k_size, self.v_size], hidden_size, dtype)
+        if self.value_from_key:
+            self.qkv = Linear([f"{p}.{q}", f"{p}.{k}"], [self.q_size, self.k_size], hidden_size, dtype)
+        else:
+            self.qkv = Linear([f"{p}.{q}", f"{p}.{k}", f"{p}.{v}"], [self.q_size, self.k_size, self.v_size], hidden_size, dtype)
+        self.rot_gain = float(getattr(self.position, "magnitude", 1.0))
         self.o = Linear([f"{p}.{o}"], [hidden_size], self.num_heads * self.vdim, dtype)
         self._mix_spec = TensorSpec(f"{p}.{mix}", (), init="zeros") if self.value_mix else None
         self.mix: Optional[torch.Tensor] = None
         suffix = spec.get("bias_suffix", ".b")
         self._bias_specs = [TensorSpec(f"{p}.{n}{suffix}", (size,), init="zeros")
-                            for n, size in ((q, self.q_size), (k, self.k_size), (v, self.v_size))] if self.has_bias else []
+                            for n, size in ((q, self.q_size), (k, self.k_size), (v, self.v_size))[:2 if self.value_from_key else 3]] if self.has_bias else []
         self._gain_specs = [TensorSpec(f"{p}.{n}", (self.dim,), keep_stored_precision=True, init="ones")
                             for n in (q_norm, k_norm)] if self.qk_norm == "gain" else []
         self._sink_spec = TensorSpec(f"{p}.{sink}", (self.num_heads,), keep_stored_precision=True, init="zeros") if self.sink == "learned" else None
@@ -168,7 +176,7 @@ class WindowAttention(Mixer):
                                       v_first, self.mix if v_first is not None else None, kv.cache if kv.writes else None,
                                       bias=self.bias, norm=self.qk_norm != "none", q_gain=self.q_gain, k_gain=self.k_gain,
                                       norm_first=self.norm_first, rot_half=getattr(self.position, "layout", "") == "half",
-                                      q_temp=self.q_temp)
+                                      q_temp=self.q_temp, value_from_key=self.value_from_key, rot_gain=self.rot_gain)
         out = torch.empty((qkv.shape[0], self.num_heads * self.vdim), dtype=qkv.dtype, device=qkv.device)
         attention_dispatch.window_attention(qkv, out, kv, ctx, self.num_heads, self.num_kv_heads, self.dim, self.vdim,
                                             self.scale, self.softcap, self.window, self.keep_first, chunked=self.chunked,
