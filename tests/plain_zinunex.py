@@ -223,3 +223,129 @@ def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], st
     for _ in range(steps):
         seq.append(int(forward(config, weights, seq)[-1].argmax()))
     return seq[len(prompt):]
+
+
+# ---- how safe the routers' choices are ------------------------------------------------------------------------------------
+def choice_margins(z, correction, top: int, groups: int, keep: int):
+    """For rows of router logits z [N, E]: the smallest amount by which a choice score (or half a group's mark) would
+    have to move to change which groups are kept or which experts are chosen, per row [N]."""
+    N, E = z.shape
+    c = torch.sigmoid(z) + correction
+    size = E // groups
+    margin = torch.full((N,), math.inf, dtype=z.dtype)
+    allowed = torch.ones(N, E, dtype=torch.bool)
+    if groups > 1:
+        marks = c.view(N, groups, size).topk(min(2, size), dim=-1).values.sum(-1)
+        ranked = marks.sort(-1, descending=True)
+        if keep < groups:
+            margin = torch.minimum(margin, (ranked.values[:, keep - 1] - ranked.values[:, keep]) / 2)
+        kept = torch.zeros(N, groups, dtype=torch.bool)
+        kept.scatter_(1, ranked.indices[:, :keep], True)
+        allowed = kept.repeat_interleave(size, dim=1)
+    ranked = c.masked_fill(~allowed, -math.inf).sort(-1, descending=True).values
+    if top < keep * size:
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])
+    return margin
+
+
+def router_margin(config: dict, weights: Dict[str, torch.Tensor], tokens) -> float:
+    """The smallest margin (see ``choice_margins``) over the sequence's tokens and layers; the tests assert that their
+    weights leave a safe one, so that an engine that rounds differently still chooses the same experts."""
+    seen: list = []
+    forward(config, weights, tokens, routers=seen)
+    worst = math.inf
+    for f, z, correction in seen:
+        r = f["router"]
+        gr = r.get("groups") or {"count": 1, "keep": 1}
+        worst = min(worst, float(choice_margins(z, correction.to(z.dtype), int(r["top"]), int(gr["count"]), int(gr["keep"])).min()))
+    return worst
+
+
+# ---- random weights for the tests -------------------------------------------------------------------------------------------
+def random_model(config: dict, seed: int, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Weights whose values are bfloat16 numbers.  The routers are made robust against rounding, so that a bfloat16
+    engine and this implementation choose the same experts: the first E columns of the embedding carry, per token id, the
+    router's logits (a router's row e reads column e, plus a little of everything else), drawn again until every layer's
+    choice has a safe margin at every size the stream's norm may have; every tensor that writes into the stream is small
+    in those columns."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = config["width"], config["vocab"]
+    mixtures = [(i, L["mlp"]) for i, L in enumerate(config["layers"]) if L.get("mlp")]
+    E_max = max([f["router"]["experts"] for _, f in mixtures] + [0])
+    assert E_max < W
+
+    def mat(o, i, gain=1.0):
+        return (torch.randn(o, i, generator=g) * gain / math.sqrt(i)).bfloat16().to(dtype)
+
+    def vec(n, around=0.0, spread=0.1):
+        return (around + spread * torch.randn(n, generator=g)).bfloat16().to(dtype)
+
+    def writer(i, gain=0.4):                         # [W, i]: output rows of the router's columns are small
+        m = torch.randn(W, i, generator=g) * gain / math.sqrt(i)
+        m[:E_max] *= 0.003
+        return m.bfloat16().to(dtype)
+
+    t: Dict[str, torch.Tensor] = {"head": mat(V, W, 2.0), "final.norm": vec(W, 1.0)}
+    corrections = {}
+    for i, f in mixtures:
+        E = f["router"]["experts"]
+        corrections[i] = (0.25 * torch.randn(E, generator=g)).bfloat16().double()
+        t[f"l{i}.mlp.correction"] = corrections[i].to(dtype)
+    embed = torch.randn(V, W, generator=g)
+    if E_max:
+        todo = torch.arange(V)
+        for _ in range(2000):
+            if not len(todo):
+                break
+            cand = ((torch.rand(len(todo), E_max, generator=g) * 2 - 1) * 1.3).bfloat16().double()
+            ok = torch.ones(len(todo), dtype=torch.bool)
+            for i, f in mixtures:
+                r = f["router"]
+                gr = r.get("groups") or {"count": 1, "keep": 1}
+                for step in range(13):                            # logits = 2 * column / rms(stream): 0.6 to 2.7
+                    lam = 0.6 * 2.0 ** (step * 0.18)
+                    ok &= choice_margins(cand[:, :r["experts"]] * lam, corrections[i], r["top"], gr["count"], gr["keep"]) > 0.05
+            embed[todo[ok], :E_max] = cand[ok].float()
+            todo = todo[~ok]
+        assert not len(todo), "no safe logits found for some token ids"
+    t["embed"] = embed.bfloat16().to(dtype)
+    side = config.get("token_side")
+    if side:
+        t["side.embed"] = torch.randn(V, len(config["layers"]) * side["dim"], generator=g).bfloat16().to(dtype)
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        t[p + "norm1"] = vec(W, 1.0)
+        if L["type"] == "latent_attention":
+            H, d, dr, dv, rk = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            t[p + "mix.q"] = mat(H * (d + dr), W, 2.0)
+            if m.get("kv_from") is None:
+                t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(rk + dr, W, 1.5), vec(rk, 1.0)
+            t[p + "mix.uk"], t[p + "mix.uv"] = mat(H * d, rk, 1.5), mat(H * dv, rk)
+            t[p + "mix.o"] = writer(H * dv)
+        else:
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            t[p + "mix.q"], t[p + "mix.k"] = mat(H * d, W, 2.0), mat(G * d, W, 1.5)
+            t[p + "mix.sink"] = vec(H, 0.0, 1.0)
+            t[p + "mix.o"] = writer(H * d)
+        f = L.get("mlp")
+        if f:
+            t[p + "norm2"] = vec(W, 1.0)
+            t[p + "norm2"][:E_max] = 1.0
+            E, ff = f["router"]["experts"], f["expert"]["ff"]
+            for e in range(E):
+                t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = mat(ff, W, 1.5), writer(ff)
+            router = torch.randn(E, W, generator=g) * 0.02 / math.sqrt(W)
+            router[:, :E_max] = 0.0
+            for e in range(E):
+                router[e, e] = 2.0
+            t[p + "mlp.router"] = router.bfloat16().to(dtype)
+            if f.get("shared"):
+                t[p + "mlp.shared.up"], t[p + "mlp.shared.down"] = mat(f["shared"]["ff"], W, 1.5), writer(f["shared"]["ff"])
+                t[p + "mlp.shared.sg"] = mat(1, W, 2.0)
+        if side:
+            t[p + "side.gate"], t[p + "side.proj"] = mat(side["dim"], W), mat(W, side["dim"])
+            gain = 0.3 + 0.05 * torch.randn(W, generator=g)
+            gain[:E_max] = 0.003
+            t[p + "side.norm"] = gain.bfloat16().to(dtype)
+    return t
