@@ -446,12 +446,12 @@ def main() -> int:
                         help="also run the reference's serving workload (1 024-token prompts, 128 outputs, 8 and 32 requests "
                              "in flight) through the engine's continuous batching")
     parser.add_argument("--designs", action="store_true",
-                        help="instead of the benchmark: the Bilolorn, Kusolorn or Desilorn design beside the Qwen3 dense decoder at equal layer sizes "
+                        help="instead of the benchmark: the Bilolorn, Kusolorn, Desilorn or Zinunex design beside the Qwen3 dense decoder at equal layer sizes "
                              "(prefill and decode throughput, every kernel of a step against its roofline; one JSON line per "
                              "design and size; see cuinfer_b200/bench_designs.py)")
     parser.add_argument("--design-sizes", default="small,large", help="with --designs: which of its sizes to run")
     parser.add_argument("--design-names", default="bilolorn,qwen3",
-                        help="with --designs: which designs to run (bilolorn, kusolorn, kusolorn_attention, desilorn, qwen3)")
+                        help="with --designs: which designs to run (bilolorn, kusolorn, kusolorn_attention, desilorn, zinunex, qwen3)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -1,4 +1,4 @@
-"""Bilolorn, Kusolorn and Desilorn beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput
+"""Bilolorn, Kusolorn, Desilorn and Zinunex beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput
 through the model runner, and the time of every kernel of a step with the share of its roofline that it reaches.
 
 ``bench.py --designs`` runs this (``--design-names kusolorn,qwen3`` chooses the designs; ``kusolorn_attention`` is
@@ -99,6 +99,25 @@ def desilorn_config(s: dict) -> dict:
             "layers": layers}
 
 
+def zinunex_config(s: dict) -> dict:
+    """Four layers: attention over a cached latent with a sliding window (Bilolorn's head sizes and latent size), two
+    layers of grouped-query attention with a sink whose values are its keys (the Qwen3 arm's head counts and head size),
+    and a second latent layer that reads the first one's cache; a mixture of ungated experts under a scored router with
+    a gated shared expert in every layer (Bilolorn's expert sizes); the per-layer token input."""
+    rot = {"base": 1000000.0, "dims": s["rot_dim"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "kv_rank": s["kv_rank"],
+              "scale": (s["dim"] + s["rot_dim"]) ** -0.5, "mask": {"size": s["window"]}, "rot": rot}
+    sink = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["head_dim"], "vdim": s["head_dim"], "scale": s["head_dim"] ** -0.5,
+            "rot": {"base": 50000.0, "dims": s["head_dim"], "scaling": {"factor": 8.0}}}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]}}
+    kinds = [("latent_attention", latent), ("attention", sink), ("attention", sink), ("latent_attention", dict(latent, kv_from=0))]
+    layers = [{"type": t, "mixer": dict(m, kv_from=i // 4 * 4) if "kv_from" in m else m, "mlp": moe}
+              for i, (t, m) in enumerate((kinds * ((s["layers"] + 3) // 4))[:s["layers"]])]
+    return {"architecture": "Zinunex", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "token_side": {"dim": s["side_dim"]}, "layers": layers}
+
+
 def qwen3_config(s: dict) -> dict:
     return dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=s["layers"], hidden_size=s["width"],
                 num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["head_dim"],
@@ -189,6 +208,15 @@ class KernelTimes:
                 rows += min(k, k - (k - n) // window * window) if chunked and window else min(k, (window + keep + n) if window else k)
             return 2.0 * pairs * heads * (qk + v), rows * (qk + v) * 2 + q.shape[0] * heads * (qk + v) * 2
 
+        def latent(q, heads, rk, dr, window):
+            """Attention over cached latent rows of rk + dr values that every head reads: all earlier keys, or the last
+            ``window``."""
+            if not window:
+                return _attention_cost(q.shape[0], heads, rk + dr, rk, (rk + dr) * 2, lq, lk)
+            flops, _ = windowed(q, heads, rk + dr, rk, window, 0)
+            rows = sum(min(k, window + n) for n, k in zip(lq, lk))
+            return flops, rows * (rk + dr) * 2 + q.shape[0] * heads * (2 * rk + dr) * 2
+
         def hyper(streams, y, write, read, norm, out, read_out=None):
             """One pass over the streams: read once, written once when a sub-layer's output is outstanding."""
             return 0.0, _nbytes(streams) * (2 if y is not None else 1) + _nbytes(y, out, read_out)
@@ -215,9 +243,10 @@ class KernelTimes:
             "latent_prep": lambda proj, q_off, rq, kv_off, rk, dr, *a, **k: (0.0, proj.shape[0] * (2 * rq + 2 * (rk + dr)) * 2),
             "qk_norm_rope_kv_write": lambda qkv, *a, **k: (0.0, 2 * _nbytes(qkv)),
             "latent_attention_mma": lambda q_abs, q, out, cache, bt, qsl, sl, ql, freq, rd, sinks, H, dn, rk, dr, *a, **k:
-                _attention_cost(q.shape[0], H, rk + dr, rk, (rk + dr) * 2, lq, lk),
+                latent(q, H, rk, dr, k.get("window", 0)),
             "latent_attention_generic": lambda q_abs, q, out, cache, bt, qsl, sl, tr, pos, freq, rd, sinks, H, dn, rk, dr, *a, **k:
-                _attention_cost(q.shape[0], H, rk + dr, rk, (rk + dr) * 2, lq, lk),
+                latent(q, H, rk, dr, k.get("window", 0)),
+            "router_scored_topk": rowwise,
             "attention_tcgen05": lambda qkv, out, cache, bt, qsl, sl, lens, nq, nkv, d, *a, **k:
                 _attention_cost(qkv.shape[0], nq, d, d, 2 * nkv * d * 2, lq, lk),
             "paged_attention_prefill": lambda qkv, out, cache, bt, qsl, sl, lens, nq, nkv, d, *a, **k:
@@ -225,8 +254,8 @@ class KernelTimes:
             "paged_attention_decode": lambda qkv, out, cache, bt, sl, nq, nkv, d, *a, **k:
                 _attention_cost(qkv.shape[0], nq, d, d, 2 * nkv * d * 2, lq, lk),
             "moe_table_feed_forward": lambda h, ids, table, gate_up, down, base, out, **kw:
-                (2.0 * h.shape[0] * table.shape[1] * 3 * (gate_up.shape[1] // 2) * h.shape[1],
-                 min(h.shape[0] * table.shape[1], gate_up.shape[0]) * 3 * (gate_up.shape[1] // 2) * h.shape[1] * 2 + 3 * _nbytes(h)),
+                (2.0 * h.shape[0] * table.shape[1] * (gate_up.shape[1] + down.shape[2]) * h.shape[1],
+                 min(h.shape[0] * table.shape[1], gate_up.shape[0]) * (gate_up.shape[1] + down.shape[2]) * h.shape[1] * 2 + 3 * _nbytes(h)),
             "gemm_generic_batched": lambda a, w, out: (2.0 * a.shape[0] * a.shape[1] * a.shape[2] * w.shape[1], _nbytes(a, w, out)),
             "gemm_tcgen05": lambda a, w, out, **k: (2.0 * a.shape[0] * a.shape[1] * w.shape[0], _nbytes(a, w, out)),
             "gemm_skinny": lambda w, out, **k: (2.0 * out.shape[0] * w.shape[0] * w.shape[1], _nbytes(w, out)),
@@ -263,7 +292,7 @@ def measure(design: str, size: str, prefill_tokens: int, batch: int, context: in
 
     s = SIZES[size]
     config = {"bilolorn": bilolorn_config, "kusolorn": kusolorn_config, "kusolorn_attention": kusolorn_attention_config,
-              "desilorn": desilorn_config, "qwen3": qwen3_config}[design](s)
+              "desilorn": desilorn_config, "zinunex": zinunex_config, "qwen3": qwen3_config}[design](s)
     pages = (batch * (context + steps + 64) + prefill_tokens) // 16 + 64
     runner = make_runner(config, pages, max_seqs=max(batch, 8), graphs=True)
     gen = torch.Generator().manual_seed(5)

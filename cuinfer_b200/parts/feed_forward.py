@@ -285,6 +285,12 @@ class RoutedExperts(FeedForward):
         self.gate_up = store.get_stacked(self._gate_up_specs).to(self.dtype).view(E, (2 if self.gated else 1) * I, H)
         self.down = store.get_stacked(self._down_specs).to(self.dtype).view(E, H, I)
         self.router.load(store)
+        rows = self.router.weight.shape[0]
+        if rows % 8:
+            # rows of zeros up to a multiple of eight: the product then takes the tensor-core and library paths that the
+            # other projections take (nothing reads the columns they produce)
+            pad = torch.zeros((8 - rows % 8, self.hidden_size), dtype=self.router.weight.dtype, device=self.router.weight.device)
+            self.router.weight = torch.cat([self.router.weight, pad]).contiguous()
         if self._correction_spec is not None:
             self.correction = store.get(self._correction_spec).float().contiguous()
         if self.shared_size:
