@@ -30,7 +30,7 @@ def linear_frequencies(base: float, dims: int, factor: float) -> List[float]:
     return [f / factor for f in plain_frequencies(base, dims)]
 
 
-def yarn_frequencies(base: float, dims: int, factor: float, original: float, fast: float, slow: float):
+def ramp_frequencies(base: float, dims: int, factor: float, original: float, fast: float, slow: float):
     """Frequencies blended between f and f / factor along a ramp over the pair index, and the number both cosine and
     sine are multiplied by."""
     def index_of(turns: float) -> float:
@@ -67,8 +67,8 @@ def rotation_of(rot: Optional[dict], kind: str):
     base, dims, sc = float(rot["base"]), int(rot["dims"]), rot.get("scaling")
     if not sc:
         return plain_frequencies(base, dims), 1.0
-    if kind == "yarn":
-        return yarn_frequencies(base, dims, float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
+    if kind == "ramp":
+        return ramp_frequencies(base, dims, float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
     return linear_frequencies(base, dims, float(sc["factor"])), 1.0
 
 
@@ -96,7 +96,7 @@ def latent_parts(h, w: Dict[str, torch.Tensor], m: dict, eps: float):
     rk, dr = m["kv_rank"], m["rot_dim"]
     down = h @ w["dkv"].T
     c = rms(down[:, :rk], eps) * w["dkv.norm"]
-    freqs, mag = rotation_of(m.get("rot"), "yarn")
+    freqs, mag = rotation_of(m.get("rot"), "ramp")
     kr = rotate(down[:, rk:].reshape(T, 1, dr), torch.arange(T), freqs, "neighbours", mag).reshape(T, dr)
     return c, kr
 
@@ -107,7 +107,7 @@ def latent_mixer(h, w: Dict[str, torch.Tensor], m: dict, eps: float, kept=None):
     H, d, dr, dv, rk = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     c, kr = kept if kept is not None else latent_parts(h, w, m, eps)
     q = (h @ w["q"].T).view(T, H, d + dr)
-    freqs, mag = rotation_of(m.get("rot"), "yarn")
+    freqs, mag = rotation_of(m.get("rot"), "ramp")
     q_rot = rotate(q[..., d:], torch.arange(T), freqs, "neighbours", mag)
     k = (c @ w["uk"].T).view(T, H, d)
     v = (c @ w["uv"].T).view(T, H, dv)

@@ -88,14 +88,14 @@ def test_rotation_laws():
                                                      (1e4, 64, 8.0, 128, 1.0, 1.0)):
         p = part(RotaryInterleaved, "rope_interleaved", theta=base, rotary_dim=dims,
                  scaling={"kind": "ramp", "factor": factor, "original": original, "fast": fast, "slow": slow})
-        freqs, mag = plain.yarn_frequencies(base, dims, factor, original, fast, slow)
+        freqs, mag = plain.ramp_frequencies(base, dims, factor, original, fast, slow)
         assert torch.allclose(p.host_frequencies().double(), torch.tensor(freqs, dtype=torch.float64), rtol=1e-6, atol=0)
         assert abs(p.magnitude - mag) < 1e-12 and abs(mag - (0.1 * math.log(factor) + 1)) < 1e-12
     p = part(RotaryHalf, "rope_half", theta=100.0, rotary_dim=8, scaling={"kind": "linear", "factor": 2.0})
     assert torch.allclose(p.host_frequencies().double(), torch.tensor(plain.linear_frequencies(100.0, 8, 2.0), dtype=torch.float64), rtol=1e-6, atol=0)
     assert p.magnitude == 1.0 and p.layout == "half"
     # the ramp really blends: the fastest pair keeps its frequency, the slowest is divided by the factor
-    freqs, _ = plain.yarn_frequencies(1e4, 64, 8.0, 128, 4.0, 0.25)
+    freqs, _ = plain.ramp_frequencies(1e4, 64, 8.0, 128, 4.0, 0.25)
     plain_f = plain.plain_frequencies(1e4, 64)
     assert freqs[0] == plain_f[0] and abs(freqs[-1] - plain_f[-1] / 8.0) < 1e-15 and any(plain_f[i] / 8 < f < plain_f[i] for i, f in enumerate(freqs))
     with pytest.raises(ValueError):

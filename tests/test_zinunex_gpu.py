@@ -311,7 +311,7 @@ def test_latent_norm_scaled_rotation_and_cache_write(dtype):
     kg = (1 + 0.3 * torch.randn(rk, generator=g)).bfloat16().double()
     positions = [0, 1, 2, 3, 1000, 1001, 70000, 5, 6]
     slots = [7, 2, 3, -1, 0, 1, 11, 10, 5]
-    freqs, mag = plain.yarn_frequencies(250.0, dims, 5.0, 48, 6.0, 0.5)
+    freqs, mag = plain.ramp_frequencies(250.0, dims, 5.0, 48, 6.0, 0.5)
     assert mag > 1.1 and len({round(f * 250.0 ** (2 * i / dims), 6) for i, f in enumerate(freqs)}) > 1, "the ramp must do something"
     cache = torch.zeros(3, 1, 1, page, rk + dr, dtype=dtype, device="cuda")
     dev = _dev(proj, dtype)
@@ -398,7 +398,7 @@ def _latent_case(dtype, H, dn, dr, rk, dims, lengths, new, page, seed, window, s
     T = len(pos)
     q_abs = torch.randn(T, H, rk, generator=g).double() * 0.3
     q = (torch.randn(T, H, dn + dr, generator=g) * 0.3).to(dtype).double()
-    freqs, mag = plain.yarn_frequencies(1000.0, dims, 4.0, 64, 8.0, 1.0) if dims else ([], 1.0)
+    freqs, mag = plain.ramp_frequencies(1000.0, dims, 4.0, 64, 8.0, 1.0) if dims else ([], 1.0)
     if sharpen is not None:            # make query t's score with key j of its request stand out for every head
         for t, j in sharpen.items():
             key = rows[treq[t]][j, 0]
