@@ -20,6 +20,11 @@
 //     more than 8 (so O is rescaled rarely, with `tcgen05.ld`/`tcgen05.st`);
 //   * a seventeenth warp's first lane issues the MMAs.
 //
+// Two options serve attention layers that keep a token's key and value side by side in one cache row and put a learned
+// number per head into the softmax's denominator: `joined` (the cache is [pages][kv heads][slots][key 128 | value 128];
+// keys and values are boxes of the same tensor map, 128 columns apart) and `sinks` (32-bit, one per query head: when the
+// two sets are merged, exp(sink) joins the denominator once, with no value).
+//
 // Every mbarrier wait is bounded; on a time-out the kernel raises the error flag, stops, frees its tensor memory
 // and returns.
 #include <type_traits>
@@ -86,7 +91,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
                          __nv_bfloat16* __restrict__ out, int out_stride, int page_size,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ query_start_loc,
                          const int* __restrict__ seq_lens, int num_requests, int nq, int nkv, float scale_log2, int window,
-                         int* __restrict__ error_flag) {
+                         int joined, const float* __restrict__ sinks, int* __restrict__ error_flag) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sQ = base;
@@ -284,7 +289,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
         const int* table = block_table + (size_t)r * table_stride;
         const int box_rows = min(page_size, kN);
         const int boxes = kN / box_rows;
-        const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+        // joined: a token's key and value lie side by side in one row of 2 x 128 values (one plane), else in two planes
+        const long long total_rows = (long long)num_pages * (joined ? 1 : 2) * nkv * page_size;
         // a tile has at most 32 boxes (16 pages of 8 slots x 2 panels): lane = box * 2 + panel.  The page number of
         // a lane's box is fetched a tile ahead, so that no copy waits for a round trip to the table.
         const int kv = warp - kMmaWarp - 1;
@@ -305,8 +311,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             if (box < nvalid) {
                 const int off = (key0 + box * box_rows) % page_size;        // not 0 only for pages longer than a tile
                 const long long row = page >= 0 && page < num_pages
-                                          ? (((long long)page * 2 + kv) * nkv + kvh) * page_size + off : total_rows;
-                tma_load_2d((kv ? sV : sK) + b * kTileBytes + panel * kPanel + box * box_rows * 128, &kv_map, bar, panel * 64, (int)row);
+                                          ? (joined ? ((long long)page * nkv + kvh) * page_size + off
+                                                    : (((long long)page * 2 + kv) * nkv + kvh) * page_size + off)
+                                          : total_rows;
+                tma_load_2d((kv ? sV : sK) + b * kTileBytes + panel * kPanel + box * box_rows * 128, &kv_map, bar,
+                            (joined ? kv * kD : 0) + panel * 64, (int)row);
             }
         };
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
@@ -459,10 +468,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, int num_pag
             const float l1 = (s_l[1][0][row_local] + s_l[1][1][row_local]) + (s_l[1][2][row_local] + s_l[1][3][row_local]);
             const float m = fmaxf(m0, m1);
             const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m);
-            const float total = l0 * w0 + l1 * w1;
+            float total = l0 * w0 + l1 * w1;
+            // a sink is a score of the row's head without key or value: it joins the denominator once, unscaled
+            float keep = 1.f;
+            if (sinks != nullptr && row_ok) {
+                const float sink = sinks[kvh * g + (grow & (g - 1))] * 1.4426950408889634f;
+                const float top = fmaxf(m, sink);
+                keep = m == -INFINITY ? 0.f : exp2f(m - top);
+                total = total * keep + exp2f(sink - top);
+            }
             // (total is at least 2^-8 for a row with a visible key and at most a few thousand)
             const float inv = total > 0.f ? __fdividef(1.f, total) : 0.f;
-            const float f0 = w0 * inv, f1 = w1 * inv;
+            const float f0 = w0 * keep * inv, f1 = w1 * keep * inv;
             const bool has1 = num_tiles > 1;        // set 1 has an accumulator only if there was a second tile
             uint32_t a[32], b[32];
             tmem_ld_32x32b_x32(lane_addr + (uint32_t)(2 * kN + cb), a);
@@ -525,7 +542,8 @@ extern "C" int cib_attention_tcgen05_supports(int head_dim, int nq, int nkv, int
 extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
                                      int page_size, const int* block_table, int table_stride, const int* query_start_loc,
                                      const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, int head_dim,
-                                     float scale, int window, int* error_flag, cudaStream_t stream) {
+                                     float scale, int window, int joined, const float* sinks, int* error_flag,
+                                     cudaStream_t stream) {
     CIB_REQUIRE(cib_attention_tcgen05_supports(head_dim, nq, nkv, page_size),
                 "attention_tcgen05: head_dim %d, %d/%d heads, page size %d are not taken (head size 128, heads per kv head dividing 128, pages of 8, 16, 32, ... slots)",
                 head_dim, nq, nkv, page_size);
@@ -534,11 +552,13 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
                 "attention_tcgen05: rows must be 16-byte aligned");
     CIB_REQUIRE(error_flag != nullptr, "attention_tcgen05: error flag missing");
     if (num_requests == 0 || num_tiles == 0) return 0;
-    // the cache as rows of one head's slot: [pages * 2 * kv heads * page_size, 128]; a box is one page x 64 columns
-    const long long total_rows = (long long)num_pages * 2 * nkv * page_size;
+    // the cache as rows of one head's slot: [pages * 2 * kv heads * page_size, 128], or, joined, [pages * kv heads *
+    // page_size, 256] with the key in the first and the value in the second half of a row; a box is one page x 64 columns
+    const long long total_rows = (long long)num_pages * (joined ? 1 : 2) * nkv * page_size;
     CIB_REQUIRE(total_rows < (1ll << 31), "attention_tcgen05: %lld cache rows do not fit a 32-bit coordinate", total_rows);
     CUtensorMap kv_map;
-    if (encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, fa::kD, fa::kD, 64,
+    const int row_values = joined ? 2 * fa::kD : fa::kD;
+    if (encode_tensor_map_bf16_2d(&kv_map, cache, (unsigned long long)total_rows, row_values, row_values, 64,
                                   page_size < fa::kN ? page_size : fa::kN, "attention_tcgen05") != 0)
         return -1;
     static SmemLimit limit;
@@ -547,7 +567,7 @@ extern "C" int cib_attention_tcgen05(const void* q, int q_stride, void* out, int
     cudaError_t e = launch_pdl(fa::attention_tcgen05_kernel, grid, dim3(fa::kThreads), (size_t)fa::kSmemBytes, stream, prompt_pdl(),
                                kv_map, num_pages, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, page_size,
                                block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv,
-                               scale * 1.4426950408889634f, window, error_flag);
+                               scale * 1.4426950408889634f, window, joined, sinks, error_flag);
     if (e != cudaSuccess) {
         set_error("attention_tcgen05: launch failed: %s", cudaGetErrorString(e));
         return -2;

@@ -102,7 +102,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_paged_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
         "cib_paged_attention_decode": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _P, ctypes.c_longlong, _P],
         "cib_paged_attention_prefill": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-        "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+        "cib_attention_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
         "cib_gemm_skinny": [_P, _I, _I, _I, _P, _I, _P, _P, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "cib_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "cib_gemm_wstream": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -866,10 +866,18 @@ def attention_tcgen05_supports(head_dim: int, num_q_heads: int, num_kv_heads: in
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens_host, num_q_heads: int,
-                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0, *, joined: bool = False,
+                      sinks: torch.Tensor | None = None) -> None:
     """bfloat16 attention for prompt portions on tcgen05 tensor cores (head size 128, pages of 8, 16, 32, ...
-    slots): scores and output accumulate in tensor memory, keys and values come page by page through TMA."""
+    slots): scores and output accumulate in tensor memory, keys and values come page by page through TMA.
+    ``cache`` is ``[pages, 2, kv heads, page, 128]`` (keys, values) or, with ``joined``, ``[pages, 1, kv heads, page, 256]``
+    with a token's key and value side by side; ``sinks`` float32 [query heads]: ``exp(sink)`` joins a row's denominator."""
     T = q.shape[0]
+    planes, row = (1, 2 * head_dim) if joined else (2, head_dim)
+    if cache.dim() != 5 or cache.shape[1] != planes or cache.shape[2] != num_kv_heads or cache.shape[4] != row:
+        raise KernelError(f"attention_tcgen05: cache must be [pages, {planes}, {num_kv_heads}, page, {row}], got {list(cache.shape)}")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_q_heads):
+        raise KernelError("attention_tcgen05: one 32-bit sink per query head")
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_tcgen05: bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or out.shape != (T, num_q_heads * head_dim) or not cache.is_contiguous():
@@ -881,7 +889,8 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32),
         _cuda(seq_lens, "seq_lens", torch.int32), len(query_lens_host), tiles, num_q_heads, num_kv_heads, head_dim,
-        float(scale), int(window), _error_flag(q.device).data_ptr(), _stream())
+        float(scale), int(window), 1 if joined else 0, _cuda(sinks, "sinks") if sinks is not None else None,
+        _error_flag(q.device).data_ptr(), _stream())
     _check(rc, "attention_tcgen05")
     note_flagged_launch()
     _count()

@@ -102,7 +102,19 @@ def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepC
     steps whose sizes the tensor-core kernel takes run there, decode steps too (the window's 64-key tiles shared out to
     several CTAs, see ``window_decode_splits``; the all-sizes kernel, a warp per token and head with one key per lane,
     measured 16 times slower at a window of 1 024 keys of 128 values); float32 and every other size run the all-sizes kernel.  ``CUINFER_B200_WINDOW_ATTENTION=generic``
-    keeps everything on the all-sizes kernel (for comparisons)."""
+    keeps everything on the all-sizes kernel (for comparisons).
+
+    A layer whose scores are plain — no cap, no distance bias, no kept first tokens, no chunks — with keys and values of
+    128 is, sink apart, the attention that the tcgen05 kernel computes: steps that are not all single tokens go there,
+    the kernel reading the joined rows and adding the sink (5 to 7 times faster than the ``mma.sync`` kernel at 2 048
+    tokens); ``CUINFER_B200_ATTENTION=mma`` keeps them on the latter."""
+    if (q.dtype == torch.bfloat16 and not _FORCE_GENERIC_WINDOW and not _FORCE_MMA and not ctx.decode_only
+            and dim == vdim and not softcap and not keep_first and not chunked and slopes is None
+            and kernels.attention_tcgen05_supports(dim, num_heads, num_kv_heads, kv.group.page_size)
+            and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and (sinks is None or sinks.dtype == torch.float32)):
+        kernels.attention_tcgen05(q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
+                                  ctx.query_lens_for_launch(), num_heads, num_kv_heads, dim, scale, window, joined=True, sinks=sinks)
+        return
     if (q.dtype == torch.bfloat16 and not _FORCE_GENERIC_WINDOW and q.stride(0) % 8 == 0
             and kernels.window_attention_mma_supports(dim, vdim, num_heads, num_kv_heads)):
         kernels.window_attention_mma(q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,

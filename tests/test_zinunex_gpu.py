@@ -465,8 +465,9 @@ def test_latent_window_on_tensor_cores(H, dn, dr, rk, dims, lengths, new, page, 
     _close(got, want, torch.float32, "latent attention with a window")
 
 
-def _sink_case(dtype, H, G, d, lengths, new, page, seed, sharpen=None, sink=None, tensor_cores=False, splits=1):
-    """Attention over cached rows [key | value] with every earlier key visible and a sink per head."""
+def _sink_case(dtype, H, G, d, lengths, new, page, seed, sharpen=None, sink=None, tensor_cores=False, splits=1, window=0):
+    """Attention over cached rows [key | value] with every earlier key visible (or the last ``window``) and a sink per
+    head.  ``tensor_cores``: False (the all-sizes kernel), True (``mma.sync``) or "tcgen05" (key and value size 128)."""
     from cuinfer_b200 import kernels
 
     g = torch.Generator().manual_seed(seed)
@@ -483,45 +484,67 @@ def _sink_case(dtype, H, G, d, lengths, new, page, seed, sharpen=None, sink=None
     scale = 0.8
     want = torch.zeros(T, H, d, dtype=torch.float64)
     for t in range(T):
-        kv = rows[treq[t]][: pos[t] + 1]
+        kv = rows[treq[t]][max(0, pos[t] - window + 1) if window else 0: pos[t] + 1]
         for h in range(H):
             s = (kv[:, h // (H // G), :d] @ q[t, h]) * scale
             m = torch.maximum(s.max(), sinks[h])
             e = torch.exp(s - m)
             want[t, h] = (e / (e.sum() + torch.exp(sinks[h] - m))) @ kv[:, h // (H // G), d:]
     out = torch.empty(T, H * d, dtype=dtype, device="cuda")
-    if tensor_cores:
+    if tensor_cores == "tcgen05":
+        assert kernels.attention_tcgen05_supports(d, H, G, page)
+        kernels.attention_tcgen05(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(qsl), _ints(lengths),
+                                  list(new), H, G, d, scale, window, joined=True, sinks=_dev(sinks, torch.float32))
+        kernels.check_error_flags(force=True)
+    elif tensor_cores:
         assert kernels.window_attention_mma_supports(d, d, H, G)
         kernels.window_attention_mma(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(qsl), _ints(lengths),
-                                     list(new), H, G, d, d, scale, 0.0, 0, 0, splits=splits, sinks=_dev(sinks, torch.float32))
+                                     list(new), H, G, d, d, scale, 0.0, window, 0, splits=splits, sinks=_dev(sinks, torch.float32))
     else:
         kernels.window_attention_generic(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(pos), _ints(treq),
-                                         H, G, d, d, scale, 0.0, 0, 0, sinks=_dev(sinks, torch.float32))
+                                         H, G, d, d, scale, 0.0, window, 0, sinks=_dev(sinks, torch.float32))
     return out.view(T, H, d), want
 
 
-@pytest.mark.parametrize("tensor_cores,dtype", [(False, torch.float32), (False, torch.bfloat16), (True, torch.bfloat16)])
+KERNELS = [(False, torch.float32), (False, torch.bfloat16), (True, torch.bfloat16), ("tcgen05", torch.bfloat16)]
+
+
+@pytest.mark.parametrize("tensor_cores,dtype", KERNELS)
 def test_sink_attention_finds_one_far_key_among_hundreds(tensor_cores, dtype):
     """The last query of a long request looks at ONE key — the first of the sequence, the last of a page, the first of
     the next, one in the middle, itself — in a prompt's portion and decoded alone (with its keys split over CTAs)."""
     n, page = 700, 16
-    d = 64 if tensor_cores else 20
-    for j in (0, 1, page - 1, page, 333, n - 2, n - 1):
-        for new, t, splits in (([1, 1], 0, 3 if tensor_cores else 1), ([40, 2], 39, 1)):
+    d = 128 if tensor_cores == "tcgen05" else 64 if tensor_cores else 20
+    for j in (0, 1, page - 1, page, 127, 128, 333, n - 2, n - 1):
+        for new, t, splits in (([1, 1], 0, 3 if tensor_cores is True else 1), ([40, 2], 39, 1)):
             got, want = _sink_case(dtype, 4, 2, d, [n, 40], new, page, 10 + j, sharpen={t: j}, tensor_cores=tensor_cores, splits=splits)
             _close(got, want, dtype, f"query at {n - 1} looking at key {j}")
             assert float(want[t].abs().max()) > 0.2, "the case does not single a key out"
 
 
-@pytest.mark.parametrize("tensor_cores,dtype", [(False, torch.float32), (False, torch.bfloat16), (True, torch.bfloat16)])
+@pytest.mark.parametrize("tensor_cores,dtype", KERNELS)
 def test_the_sink_takes_weight_and_gives_nothing(tensor_cores, dtype):
     big = torch.tensor([30.0, -30.0, 0.5, -1.0], dtype=torch.float64)
-    d = 64 if tensor_cores else 12
+    d = 128 if tensor_cores == "tcgen05" else 64 if tensor_cores else 12
     for lengths, new in (([21], [21]), ([300, 5], [1, 1])):
         got, want = _sink_case(dtype, 4, 1, d, lengths, new, 4 if not tensor_cores else 16, 5, sink=big, tensor_cores=tensor_cores)
         _close(got, want, dtype, "sinks of +30, -30 and small ones")
         assert float(got[:, 0].float().abs().max()) < 1e-6, "a sink far above every score leaves no weight for the keys"
         assert float(got[:, 1].float().abs().max()) > 1e-2
+
+
+@pytest.mark.parametrize("H,G", [(4, 2), (3, 3), (8, 1), (16, 2)])
+def test_joined_rows_and_sinks_on_tcgen05(H, G):
+    """The tcgen05 kernel over rows [key | value] of one plane with a sink per head: prompts beside single tokens, several
+    query tiles a request, pages out of order, and a window whose pages behind it are kept or not."""
+    dtype = torch.bfloat16
+    for window in (0, 200, 33):
+        got, want = _sink_case(dtype, H, G, 128, [300, 1, 97, 410], [300, 1, 40, 3], 16, 3 * H + window, tensor_cores="tcgen05", window=window)
+        _close(got, want, dtype, f"tcgen05 attention over joined rows, window {window}")
+    n, window = 260, 70
+    for j in (n - window, n - window - 1, 0, 127, 128, n - 1):
+        got, want = _sink_case(dtype, H, G, 128, [n, 50], [100, 2], 16, j, sharpen={99: j}, tensor_cores="tcgen05", window=window)
+        _close(got, want, dtype, f"query {n - 1} with key {j} standing out")
 
 
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 2, 1), (6, 2, 3, 2), (5, 2, 1, 1), (4, 4, 2, 2), (6, 1, 6, 2), (130, 7, 10, 3),
