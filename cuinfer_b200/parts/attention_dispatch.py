@@ -91,6 +91,11 @@ def window_decode_splits(ctx: StepContext, num_kv_heads: int, window: int, keep_
 
 
 _FORCE_GENERIC_WINDOW = os.environ.get("CUINFER_B200_WINDOW_ATTENTION", "") == "generic"
+# From how many (request, key head) pairs on a step of single tokens runs on the tcgen05 kernel too — one CTA per pair
+# walks the keys in tiles of 128 — instead of the kernel that shares a pair's key tiles out to several CTAs.  Measured
+# a call at 2 084 / 8 192 keys of 8 key heads: 1 request 37 / 124 us against 31 / 82; 8 requests 38 / 125 against 53 /
+# 163; 64 requests 151 / 494 against 438 / 1 669.
+TCGEN05_DECODE_MIN_CTAS = 48
 
 
 def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int, num_kv_heads: int,
@@ -107,8 +112,10 @@ def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepC
     A layer whose scores are plain — no cap, no distance bias, no kept first tokens, no chunks — with keys and values of
     128 is, sink apart, the attention that the tcgen05 kernel computes: steps that are not all single tokens go there,
     the kernel reading the joined rows and adding the sink (5 to 7 times faster than the ``mma.sync`` kernel at 2 048
-    tokens); ``CUINFER_B200_ATTENTION=mma`` keeps them on the latter."""
-    if (q.dtype == torch.bfloat16 and not _FORCE_GENERIC_WINDOW and not _FORCE_MMA and not ctx.decode_only
+    tokens), and so do steps of single tokens with enough requests to fill the GPU without splitting keys (see
+    ``TCGEN05_DECODE_MIN_CTAS``); ``CUINFER_B200_ATTENTION=mma`` keeps them on the ``mma.sync`` kernel."""
+    if (q.dtype == torch.bfloat16 and not _FORCE_GENERIC_WINDOW and not _FORCE_MMA
+            and (not ctx.decode_only or ctx.num_requests * num_kv_heads >= TCGEN05_DECODE_MIN_CTAS)
             and dim == vdim and not softcap and not keep_first and not chunked and slopes is None
             and kernels.attention_tcgen05_supports(dim, num_heads, num_kv_heads, kv.group.page_size)
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and (sinks is None or sinks.dtype == torch.float32)):
