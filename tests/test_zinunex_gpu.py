@@ -219,6 +219,21 @@ def test_steps_through_cuda_graphs(folders, dtype, tmp_path):
     assert runner.model.capturable and runner.graph_steps + runner.step_graph_replays > 0
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_many_requests_decoding_together(folders, graphs, tmp_path):
+    """Thirteen requests decode side by side: enough (request, key head) pairs for the layer with heads of 128 to take
+    the tcgen05 kernel in steps of single tokens too, eagerly and from a decode graph whose bucket has padding rows."""
+    cfg = folders["wide"][0]
+    requests = _requests(cfg, [20 + 3 * i for i in range(13)], seed=8)
+    heads = {rid: len(t) - 6 for rid, t in requests.items()}
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": t[:heads[rid]], "want": list(range(heads[rid]))} for rid, t in requests.items()], "end": []}]
+    for k in range(6):
+        steps.append({"step": k + 1, "entries": [{"id": rid, "tokens": [t[heads[rid] + k]], "want": [0]} for rid, t in requests.items()],
+                      "end": list(requests) if k == 5 else []})
+    runner = _check(folders, "wide", "bfloat16", steps, requests, tmp_path, cuda_graph=graphs, passes=2 if graphs else 1, max_live=16)
+    assert not graphs or runner.graph_steps > 0
+
+
 def test_the_stream_after_every_layer(folders):
     """The residual stream after each layer of a short prompt, in 32 bits, against the plain model's."""
     from cuinfer_b200.engine import replay
