@@ -20,7 +20,9 @@
 namespace cib {
 
 constexpr int kMoeWarps = 8;
-constexpr int kMoeOutsPerBlock = 64;
+// outputs a block computes: 32 for rows of up to 2 048 values (more blocks: a decode step of eight tokens is 80 / 150 us a
+// call instead of 94 / 170 at widths of 1 024 / 2 048), 64 for longer ones (a block's copy of its input row is shared by more)
+static inline int moe_outs_per_block(int width) { return width > 2048 ? 64 : 32; }
 
 struct ExpertAct {
     int kind;        // 0: silu(gate) * up;  1: the clamped gate described above;  2: no gate, relu(up)^2;  -1: nothing
@@ -91,11 +93,64 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const __nv_bfloat16* __r
     return warp_sum(s);
 }
 
+// Two rows at once, each against its own vector: the loads of both rows are issued before either is used, so a lane
+// keeps eight 16-byte loads in flight instead of four (a decode step has too few warps an SM for four to fill the
+// memory pipe: two rows at a time took a call of the large experts from 180 to 107 us).  Every row is summed in the
+// order `dot_row` sums it, so the results are the same to the last bit.
+template <typename T>
+__device__ __forceinline__ void dot_rows2(const T* __restrict__ w0, const float* __restrict__ x0, const T* __restrict__ w1,
+                                          const float* __restrict__ x1, int n, int lane, float& r0, float& r1) {
+    r0 = dot_row(w0, x0, n, lane);
+    r1 = dot_row(w1, x1, n, lane);
+}
+__device__ __forceinline__ float dot_chunk(const uint4& v, const float* __restrict__ xs, float s) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        s = fmaf(__low2float(h[k]), xs[2 * k], s);
+        s = fmaf(__high2float(h[k]), xs[2 * k + 1], s);
+    }
+    return s;
+}
+template <>
+__device__ __forceinline__ void dot_rows2<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w0, const float* __restrict__ x0,
+                                                         const __nv_bfloat16* __restrict__ w1, const float* __restrict__ x1, int n,
+                                                         int lane, float& r0, float& r1) {
+    if ((n & 7) != 0 || ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1)) & 15) != 0) {
+        r0 = dot_row(w0, x0, n, lane);
+        r1 = dot_row(w1, x1, n, lane);
+        return;
+    }
+    const uint4* a8 = reinterpret_cast<const uint4*>(w0);
+    const uint4* b8 = reinterpret_cast<const uint4*>(w1);
+    const int chunks = n >> 3;
+    float s0 = 0.f, s1 = 0.f;
+    int c = lane;
+    for (; c + 96 < chunks; c += 128) {
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = __ldg(a8 + c + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) b[u] = __ldg(b8 + c + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s0 = dot_chunk(a[u], x0 + (c + 32 * u) * 8, s0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s1 = dot_chunk(b[u], x1 + (c + 32 * u) * 8, s1);
+    }
+    for (; c < chunks; c += 32) {
+        const uint4 a = __ldg(a8 + c), b = __ldg(b8 + c);
+        s0 = dot_chunk(a, x0 + c * 8, s0);
+        s1 = dot_chunk(b, x1 + c * 8, s1);
+    }
+    r0 = warp_sum(s0);
+    r1 = warp_sum(s1);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_table_gate_up_kernel(const T* __restrict__ h, int h_stride, const int* __restrict__ ids,
                          const int* __restrict__ table, int vocab, int top, int experts,
-                         const T* __restrict__ gate_up, T* __restrict__ act, int width, int ff, ExpertAct fn) {
+                         const T* __restrict__ gate_up, T* __restrict__ act, int width, int ff, ExpertAct fn, int outs) {
     extern __shared__ float hs[];
     const int t = blockIdx.x / top, k = blockIdx.x % top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,14 +162,27 @@ moe_table_gate_up_kernel(const T* __restrict__ h, int h_stride, const int* __res
     const bool gated = fn.gated();
     const T* wg = gate_up + (size_t)(ok ? e : 0) * (gated ? 2 : 1) * ff * width;
     const T* wu = wg + (size_t)ff * width;
-    const int j0 = blockIdx.y * kMoeOutsPerBlock;
-    for (int j = j0 + warp; j < min(ff, j0 + kMoeOutsPerBlock); j += kMoeWarps) {
-        float v = 0.f;
-        if (ok) {
-            const float g = dot_row(wg + (size_t)j * width, hs, width, lane);
-            v = gated ? fn(g, dot_row(wu + (size_t)j * width, hs, width, lane)) : fn.single(g);
+    const int j0 = blockIdx.y * outs, j_end = min(ff, j0 + outs);
+    T* dst = act + ((size_t)t * top + k) * ff;
+    if (gated) {                                      // a gate row and its up row together
+        for (int j = j0 + warp; j < j_end; j += kMoeWarps) {
+            float g = 0.f, u = 0.f;
+            if (ok) dot_rows2(wg + (size_t)j * width, hs, wu + (size_t)j * width, hs, width, lane, g, u);
+            if (lane == 0) dst[j] = from_f32<T>(ok ? fn(g, u) : 0.f);
         }
-        if (lane == 0) act[((size_t)t * top + k) * ff + j] = from_f32<T>(v);
+        return;
+    }
+    for (int j = j0 + warp; j < j_end; j += 2 * kMoeWarps) {          // two rows of the one matrix together
+        const int j2 = j + kMoeWarps;
+        float a = 0.f, b = 0.f;
+        if (ok) {
+            if (j2 < j_end) dot_rows2(wg + (size_t)j * width, hs, wg + (size_t)j2 * width, hs, width, lane, a, b);
+            else a = dot_row(wg + (size_t)j * width, hs, width, lane);
+        }
+        if (lane == 0) {
+            dst[j] = from_f32<T>(ok ? fn.single(a) : 0.f);
+            if (j2 < j_end) dst[j2] = from_f32<T>(ok ? fn.single(b) : 0.f);
+        }
     }
 }
 
@@ -123,7 +191,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, const int* __restrict__ table, int vocab,
                       int top, int experts, const T* __restrict__ down, const T* __restrict__ base, int base_stride,
                       float weight, const float* __restrict__ weights, const float* __restrict__ base_gate, int base_gate_stride,
-                      T* __restrict__ out, int width, int ff) {
+                      T* __restrict__ out, int width, int ff, int outs) {
     extern __shared__ float as[];                       // [top][ff]
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,19 +199,30 @@ moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, co
     __syncthreads();
     const int id = ids ? ids[t] : t;
     const bool id_ok = id >= 0 && id < vocab;
-    const int i0 = blockIdx.y * kMoeOutsPerBlock;
-    for (int i = i0 + warp; i < min(width, i0 + kMoeOutsPerBlock); i += kMoeWarps) {
-        float sum = 0.f;
+    const int i0 = blockIdx.y * outs, i_end = min(width, i0 + outs);
+    const float bg = base && base_gate ? 1.f / (1.f + expf(-base_gate[(size_t)t * base_gate_stride])) : 1.f;
+    for (int i = i0 + warp; i < i_end; i += 2 * kMoeWarps) {           // two outputs together
+        const int i2 = i + kMoeWarps;
+        float sum[2] = {0.f, 0.f};
         for (int k = 0; k < top; ++k) {
             const int e = id_ok ? table[(size_t)id * top + k] : -1;
             if (e < 0 || e >= experts) continue;
-            const float dot = dot_row(down + ((size_t)e * width + i) * ff, as + k * ff, ff, lane);
-            sum += weights ? weights[(size_t)t * top + k] * dot : dot;
+            float d0, d1 = 0.f;
+            if (i2 < i_end) dot_rows2(down + ((size_t)e * width + i) * ff, as + k * ff, down + ((size_t)e * width + i2) * ff, as + k * ff, ff, lane, d0, d1);
+            else d0 = dot_row(down + ((size_t)e * width + i) * ff, as + k * ff, ff, lane);
+            const float wk = weights ? weights[(size_t)t * top + k] : 1.f;
+            sum[0] += wk * d0;
+            sum[1] += wk * d1;
         }
         if (lane == 0) {
-            float v = weights ? sum : sum * weight;
-            if (base) v += to_f32(base[(size_t)t * base_stride + i]) * (base_gate ? 1.f / (1.f + expf(-base_gate[(size_t)t * base_gate_stride])) : 1.f);
-            out[(size_t)t * width + i] = from_f32<T>(v);
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int o = r == 0 ? i : i2;
+                if (o >= i_end) continue;
+                float v = weights ? sum[r] : sum[r] * weight;
+                if (base) v += to_f32(base[(size_t)t * base_stride + o]) * bg;
+                out[(size_t)t * width + o] = from_f32<T>(v);
+            }
         }
     }
 }
@@ -158,12 +237,13 @@ extern "C" int cib_moe_table_gate_up(const void* h, int h_stride, int dtype, con
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
     CIB_REQUIRE(width <= 12 * 1024, "moe_table: width %d too large for this kernel", width);
     if (num_tokens == 0) return 0;
-    dim3 grid(num_tokens * top, (ff + kMoeOutsPerBlock - 1) / kMoeOutsPerBlock);
+    const int outs = moe_outs_per_block(width);
+    dim3 grid(num_tokens * top, (ff + outs - 1) / outs);
     const size_t smem = (size_t)width * sizeof(float);
     if (dtype == kF32)
-        moe_table_gate_up_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)h, h_stride, ids, table, vocab, top, experts, (const float*)gate_up, (float*)act, width, ff, ExpertAct{act_kind, limit});
+        moe_table_gate_up_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)h, h_stride, ids, table, vocab, top, experts, (const float*)gate_up, (float*)act, width, ff, ExpertAct{act_kind, limit}, outs);
     else if (dtype == kBF16)
-        moe_table_gate_up_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)h, h_stride, ids, table, vocab, top, experts, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, width, ff, ExpertAct{act_kind, limit});
+        moe_table_gate_up_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)h, h_stride, ids, table, vocab, top, experts, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, width, ff, ExpertAct{act_kind, limit}, outs);
     else
         CIB_REQUIRE(false, "moe_table: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("moe_table_gate_up");
@@ -177,12 +257,13 @@ extern "C" int cib_moe_table_down(const void* act, int dtype, const int* ids, co
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
     CIB_REQUIRE((size_t)top * ff <= 12 * 1024, "moe_table: %d x %d activations too large for this kernel", top, ff);
     if (num_tokens == 0) return 0;
-    dim3 grid(num_tokens, (width + kMoeOutsPerBlock - 1) / kMoeOutsPerBlock);
+    const int outs = moe_outs_per_block(width);
+    dim3 grid(num_tokens, (width + outs - 1) / outs);
     const size_t smem = (size_t)top * ff * sizeof(float);
     if (dtype == kF32)
-        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, base_gate, base_gate_stride, (float*)out, width, ff);
+        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, base_gate, base_gate_stride, (float*)out, width, ff, outs);
     else if (dtype == kBF16)
-        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, weights, base_gate, base_gate_stride, (__nv_bfloat16*)out, width, ff);
+        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, weights, base_gate, base_gate_stride, (__nv_bfloat16*)out, width, ff, outs);
     else
         CIB_REQUIRE(false, "moe_table: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("moe_table_down");
