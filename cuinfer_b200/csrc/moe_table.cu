@@ -255,11 +255,17 @@ extern "C" int cib_moe_table_down(const void* act, int dtype, const int* ids, co
                                   const float* weights, const float* base_gate, int base_gate_stride, void* out, int num_tokens,
                                   int width, int ff, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
-    CIB_REQUIRE((size_t)top * ff <= 12 * 1024, "moe_table: %d x %d activations too large for this kernel", top, ff);
+    CIB_REQUIRE((size_t)top * ff <= 50 * 1024, "moe_table: %d x %d activations too large for this kernel", top, ff);
     if (num_tokens == 0) return 0;
     const int outs = moe_outs_per_block(width);
     dim3 grid(num_tokens, (width + outs - 1) / outs);
-    const size_t smem = (size_t)top * ff * sizeof(float);
+    const size_t smem = (size_t)top * ff * sizeof(float);        // a token's activations of all its experts, 32-bit
+    if (smem > 48 * 1024) {
+        static SmemLimit limit_f32, limit_bf16;
+        const int rc = dtype == kF32 ? raise_smem_limit(limit_f32, moe_table_down_kernel<float>, 200 * 1024, "moe_table_down")
+                                     : raise_smem_limit(limit_bf16, moe_table_down_kernel<__nv_bfloat16>, 200 * 1024, "moe_table_down");
+        if (rc != 0) return rc;
+    }
     if (dtype == kF32)
         moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, base_gate, base_gate_stride, (float*)out, width, ff, outs);
     else if (dtype == kBF16)

@@ -619,7 +619,7 @@ def test_scored_router_ties_go_to_the_lower_index():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,ff,E,top,T", [(72, 36, 5, 2, 9), (64, 32, 3, 3, 300), (128, 96, 9, 1, 700), (96, 160, 4, 2, 77)])
+@pytest.mark.parametrize("W,ff,E,top,T", [(72, 36, 5, 2, 9), (64, 32, 3, 3, 300), (128, 96, 9, 1, 700), (96, 160, 4, 2, 77), (40, 2600, 6, 5, 3)])
 def test_experts_without_a_gate_and_a_gated_shared_expert(dtype, W, ff, E, top, T):
     """``sum_k w_k down_e(relu(up_e h)^2) + sigmoid(g) base``: rows by token and choice, and grouped by expert on the
     tensor cores (from 128 rows of bfloat16 on), with an expert that gets no row and a choice of -1."""
